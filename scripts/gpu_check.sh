@@ -21,7 +21,7 @@ if [ "${1:-}" = "ncu" ] || [ "${2:-}" = "ncu" ]; then
       --log-file gpurun_out/launches.csv python bench.py $BARGS > gpurun_out/ncu_launches.log 2>&1
   echo "ncu launches exit $?"
   timeout 600 python bench.py $BARGS > gpurun_out/bench_small2.json 2> gpurun_out/bench_small2.err &&
-  timeout 1200 ncu --set full --clock-control none --import-source on -k regex:"stream_decode|mega_decode" -s 9 -c 1 \
+  timeout 1200 ncu --set full --clock-control none -k regex:"stream_decode|mega_decode" -s 9 -c 1 \
       -o gpurun_out/mega_full -f python bench.py $BARGS > gpurun_out/ncu_full.log 2>&1
   echo "ncu full exit $?"
   ls -la gpurun_out/ | tail -8

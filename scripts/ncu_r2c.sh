@@ -9,8 +9,8 @@ timeout 600 ncu --metrics gpu__time_duration.sum --clock-control none --csv --lo
 echo "prefill launch list exit $?"
 timeout 600 ncu --metrics gpu__time_duration.sum --clock-control none --csv --log-file gpurun_out/r02_batch_launches.csv python scripts/batch_profile.py > /dev/null 2>&1
 echo "batch launch list exit $?"
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:dequant_gemm_umma2 -s 40 -c 2 -o gpurun_out/r02_gemm2_full -f python scripts/prefill_profile.py 2048 > gpurun_out/ncu_gemm2.log 2>&1
+timeout 900 ncu --set full --clock-control none -k regex:dequant_gemm_umma2 -s 40 -c 2 -o gpurun_out/r02_gemm2_full -f python scripts/prefill_profile.py 2048 > gpurun_out/ncu_gemm2.log 2>&1
 echo "gemm2 full exit $?"
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:prefill_attn_umma -s 2 -c 1 -o gpurun_out/r02_attn_full -f python scripts/prefill_profile.py 2048 > gpurun_out/ncu_attn.log 2>&1
+timeout 900 ncu --set full --clock-control none -k regex:prefill_attn_umma -s 2 -c 1 -o gpurun_out/r02_attn_full -f python scripts/prefill_profile.py 2048 > gpurun_out/ncu_attn.log 2>&1
 echo "attn full exit $?"
 ls -la gpurun_out/*.ncu-rep
