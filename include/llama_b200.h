@@ -239,6 +239,75 @@ B200_API int b200_batch_counts(b200_batch* batch, int* active, int* pending, int
                                uint64_t* decode_rows);
 B200_API const char* b200_batch_last_error(b200_batch* batch);   /* message of the most recent ERROR event */
 
+/* ---- layer-program models ------------------------------------------------
+ * A decoder whose layers are listed one by one, each with its own token mixer, instead of one repeated transformer block.  A context
+ * made by b200_ctx_create_layers is driven through the SAME entry points as every other context -- b200_ctx_upload_tensor /
+ * b200_ctx_finalize, b200_prefill / b200_forward / b200_decode_batch / b200_decode_batch_greedy / b200_decode_greedy, b200_reset /
+ * b200_position, b200_get_hidden, b200_batch_* -- plus b200_step below.  A sequence slot then holds, per layer RUN (a layer inside
+ * the repeated range runs `loop_times` times, every pass on a state of its own): the K/V rows of a windowed attention, the f32
+ * matrix state of a recurrent mixer, the last inputs of its short convolutions.  Slot memory is taken at a slot's first token
+ * and goes back to a pool on b200_reset.
+ *
+ * Mixers (csrc/layerprog.cu; all constants are fields, nothing is fixed to one model):
+ *   B200_MIX_WINDOW_MEMORY  two branches on the same normed input, summed with attn_scale / mem_scale:
+ *        - softmax attention over a sliding window that also keeps the first `keep_first` positions visible
+ *          (key j visible from i iff j <= i and (i - j < window or j < keep_first)), grouped K/V heads, optional per-head RMS
+ *          norm of q and k (qk_norm), no rotation, optional sigmoid output gate (out_gate), separate q/k and v head sizes;
+ *        - a matrix memory with exponential input gate, sigmoid forget gate (both soft-capped: cap * tanh(z / cap)) and a
+ *          running-maximum stabiliser that starts at 0; read-out normalised by max(|n.q|, exp(-m)) + 1e-6, per-head unit RMS,
+ *          channel weight, sigmoid output gate.
+ *   B200_MIX_GATED_DELTA    gated delta rule: causal depthwise convolutions (conv taps) + SiLU on q, k, v, unit-length q and k
+ *          (q also times dim^-1/2), per-head write strength sigmoid(.) and decay exp(-exp(A_log) * softplus(. + dt_bias)),
+ *          S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q;  per-head RMS norm with a shared weight, SiLU gate.
+ * Feed-forward: none (ff = 0) or W_down act(W_up h) with act = relu(z)^2.
+ * Embedding: row * embed_scale (+ sinusoidal position vector, pos_sinusoid); logits = head . norm(x) * logit_scale.
+ * compute: 0 = bf16 weights and GEMM operands with f32 accumulation (residual stream, norms, softmax, gates and every recurrent
+ * state stay f32), 1 = everything in f32 (FMA, no reduced-precision matrix mode). */
+enum { B200_MIX_WINDOW_MEMORY = 1, B200_MIX_GATED_DELTA = 2 };
+enum { B200_COMPUTE_BF16 = 0, B200_COMPUTE_F32 = 1 };
+enum { B200_TYPE_BF16 = 30 };   /* ggml's id; accepted by layer-program contexts only */
+typedef struct b200_window_attn_desc {
+    int32_t heads, kv_heads, dim, vdim;
+    int32_t window, keep_first;
+    float scale;
+    int32_t qk_norm, out_gate;
+} b200_window_attn_desc;
+typedef struct b200_matrix_memory_desc {
+    int32_t heads, dim, vdim;
+    float gate_cap;
+} b200_matrix_memory_desc;
+typedef struct b200_gated_delta_desc {
+    int32_t heads, kv_heads, dim, vdim, conv;
+} b200_gated_delta_desc;
+typedef struct b200_layer_desc {
+    int32_t mixer;                   /* B200_MIX_* */
+    b200_window_attn_desc attn;      /* WINDOW_MEMORY */
+    b200_matrix_memory_desc mem;     /* WINDOW_MEMORY */
+    float attn_scale, mem_scale;     /* WINDOW_MEMORY: weights of the two branches in the sum */
+    b200_gated_delta_desc delta;     /* GATED_DELTA */
+    int32_t ff;                      /* feed-forward width, 0 = the layer has no second sublayer */
+} b200_layer_desc;
+typedef struct b200_program_desc {
+    int32_t width, vocab, n_layers;
+    int32_t max_seq_len, max_batch;
+    float norm_eps, embed_scale, logit_scale;
+    int32_t pos_sinusoid;                       /* 1 = add the sinusoidal position vector to the embedding */
+    int32_t loop_start, loop_stop, loop_times;  /* layers [start, stop) run `times` times in a row; a step vector per pass */
+    int32_t compute;                            /* B200_COMPUTE_* */
+} b200_program_desc;
+B200_API int b200_ctx_create_layers(const b200_program_desc* prog, const b200_layer_desc* layers, int device, b200_ctx** out);
+/* One batch of token runs: run i continues sequence slot seqs[i] with lens[i] tokens (concatenated in `tokens`).  want_rows are
+ * indices into the concatenated rows whose logits are asked for; logits_out receives n_want x vocab f32 (both may be NULL / 0).
+ * b200_prefill, b200_forward and b200_decode_batch are this call with one run, one token, or one token per run. */
+B200_API int b200_step(b200_ctx* ctx, int n_runs, const int* seqs, const int* lens, const uint32_t* tokens, const int* want_rows,
+                       int n_want, float* logits_out);
+/* Number of layer runs of a layer-program context (b200_get_hidden's `layer` counts runs there: 0 = embedding, k = after run k);
+ * taps of the last b200_step's FIRST run are kept when B200_TAPS=1: b200_get_taps copies [n_layer_runs][len][width] f32. */
+B200_API int b200_ctx_layer_runs(b200_ctx* ctx, int* out);
+B200_API int b200_get_taps(b200_ctx* ctx, float* out, size_t cap_floats);
+/* Slot manager of a layer-program context: slots that own a cache / state block now, blocks waiting in the pool for reuse. */
+B200_API int b200_ctx_pool_counts(b200_ctx* ctx, int* live, int* pooled);
+
 /* GpuInference::reset / position (backend/mod.rs:292-295). */
 B200_API int b200_reset(b200_ctx* ctx, int seq);
 B200_API int b200_position(b200_ctx* ctx, int seq, uint64_t* out);

@@ -89,9 +89,44 @@ class BatchEvent(C.Structure):
                 ("prompt_tokens", C.c_int32), ("completion_tokens", C.c_int32)]
 
 
+class WindowAttnDesc(C.Structure):
+    """b200_window_attn_desc (include/llama_b200.h)"""
+    _fields_ = [("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("window", C.c_int32),
+                ("keep_first", C.c_int32), ("scale", C.c_float), ("qk_norm", C.c_int32), ("out_gate", C.c_int32)]
+
+
+class MatrixMemoryDesc(C.Structure):
+    """b200_matrix_memory_desc"""
+    _fields_ = [("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("gate_cap", C.c_float)]
+
+
+class GatedDeltaDesc(C.Structure):
+    """b200_gated_delta_desc"""
+    _fields_ = [("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("conv", C.c_int32)]
+
+
+class LayerDesc(C.Structure):
+    """b200_layer_desc"""
+    _fields_ = [("mixer", C.c_int32), ("attn", WindowAttnDesc), ("mem", MatrixMemoryDesc), ("attn_scale", C.c_float),
+                ("mem_scale", C.c_float), ("delta", GatedDeltaDesc), ("ff", C.c_int32)]
+
+
+class ProgramDesc(C.Structure):
+    """b200_program_desc"""
+    _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("max_seq_len", C.c_int32),
+                ("max_batch", C.c_int32), ("norm_eps", C.c_float), ("embed_scale", C.c_float), ("logit_scale", C.c_float),
+                ("pos_sinusoid", C.c_int32), ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32),
+                ("compute", C.c_int32)]
+
+
+MIX_WINDOW_MEMORY, MIX_GATED_DELTA = 1, 2
+COMPUTE_BF16, COMPUTE_F32 = 0, 1
+BF16 = 30   # ggml's id; layer-program contexts only
+
+
 def build(verbose=False):
     """Compile csrc/ into libllama_b200.so with nvcc for sm_100a (cross-compiles without a GPU)."""
-    cmd = ["make", "-C", os.path.join(_HERE, "csrc")] + ([] if verbose else ["-s"])
+    cmd = ["make", "-j2", "-C", os.path.join(_HERE, "csrc")] + ([] if verbose else ["-s"])
     subprocess.check_call(cmd)
     return LIB_PATH
 
@@ -198,6 +233,11 @@ def lib():
     L.b200_op_rope.argtypes = [fp, fp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int]
     L.b200_op_attention_cached.argtypes = [fp, fp, fp, fp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int]
     L.b200_op_attention.argtypes = [fp, fp, fp, fp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]
+    L.b200_ctx_create_layers.argtypes = [C.POINTER(ProgramDesc), C.POINTER(LayerDesc), C.c_int, C.POINTER(vp)]
+    L.b200_step.argtypes = [vp, C.c_int, i32p, i32p, u32p, i32p, C.c_int, fp]
+    L.b200_ctx_layer_runs.argtypes = [vp, i32p]
+    L.b200_get_taps.argtypes = [vp, fp, C.c_size_t]
+    L.b200_ctx_pool_counts.argtypes = [vp, i32p, i32p]
     _lib = L
     return L
 
@@ -687,10 +727,10 @@ class GpuOnlyInference:
         return ("f32", "int8")[v.value]
 
     def path(self):
-        """Decode path chosen at finalize: "graph" | "mega" | "stream" | "stream2"."""
+        """Decode path chosen at finalize: "graph" | "mega" | "stream" | "stream2"; "layers" for a layer-program context."""
         v = C.c_int(0)
         _check(lib().b200_ctx_path(self._h, C.byref(v)))
-        return ("graph", "mega", "stream", "stream2")[v.value]
+        return ("graph", "mega", "stream", "stream2", "layers")[v.value]
 
     def watchdog(self):
         """The eight watchdog words of the megakernel paths (all zero = no bounded wait ever gave up); clears them."""
@@ -786,6 +826,98 @@ class GpuOnlyInference:
         return ms.value, nbytes.value
 
 
+class LayerProgramInference(GpuOnlyInference):
+    """A layer-program context (b200_ctx_create_layers): a decoder given as a list of layers with their own token mixers.  Same
+    surface as GpuOnlyInference -- forward / prefill_token / forward_batch / reset / position / decode_batch(_greedy) /
+    decode_greedy, and BatchedEngine on top -- plus step(): one batch of token runs with logits at chosen rows.
+
+    program: dict of ProgramDesc fields; layers: list of dicts {"mixer", "attn", "mem", "attn_scale", "mem_scale", "delta", "ff"}
+    (sub-dicts hold the fields of the matching *Desc); tensors: name -> (ggml_type, ne, ndarray) with ne[0] = in_features;
+    feeder(upload) may stream them instead."""
+
+    def __init__(self, program: dict, layers: list, tensors: dict = None, device=0, taps=False, feeder=None):
+        L = lib()
+        if device_count() == 0:
+            raise NotAvailable("cuda-b200: no CUDA device (this backend has no CPU fallback)")
+        pd = ProgramDesc()
+        for k, v in program.items():
+            if k not in dict(ProgramDesc._fields_):
+                raise InvalidArgument(f"unknown program desc field {k}")
+            setattr(pd, k, v)
+        pd.n_layers = len(layers)
+        arr = (LayerDesc * len(layers))()
+        for i, ld in enumerate(layers):
+            for k, v in ld.items():
+                if k not in dict(LayerDesc._fields_):
+                    raise InvalidArgument(f"unknown layer desc field {k}")
+                if isinstance(v, dict):
+                    sub = getattr(arr[i], k)
+                    for kk, vv in v.items():
+                        if kk not in dict(type(sub)._fields_):
+                            raise InvalidArgument(f"unknown {k} desc field {kk}")
+                        setattr(sub, kk, vv)
+                else:
+                    setattr(arr[i], k, v)
+        self.program = {k: getattr(pd, k) for k, _ in ProgramDesc._fields_}
+        self.desc = {"hidden": pd.width, "vocab": pd.vocab, "max_seq_len": pd.max_seq_len, "max_batch": pd.max_batch}
+        self.world, self.rank, self.expert_parallel = 1, 0, False
+        self.vocab = pd.vocab
+        h = C.c_void_p()
+        old = os.environ.get("B200_TAPS")
+        os.environ["B200_TAPS"] = "1" if taps else "0"
+        try:
+            _check(L.b200_ctx_create_layers(C.byref(pd), arr, int(device), C.byref(h)))
+        finally:
+            if old is None:
+                os.environ.pop("B200_TAPS", None)
+            else:
+                os.environ["B200_TAPS"] = old
+        self._h = h
+        try:
+            for name, (t, ne, data) in (tensors or {}).items():
+                self.upload_tensor(name, t, ne, data)
+            if feeder is not None:
+                feeder(self.upload_tensor)
+            _check(L.b200_ctx_finalize(self._h))
+        except Exception:
+            self.close()
+            raise
+
+    def step(self, runs, want=None):
+        """runs: [(seq, tokens)], every run continues its slot; want: row indices into the concatenated tokens (default: none).
+        Returns the logits of the wanted rows, [len(want), vocab] (None when nothing is wanted)."""
+        seqs = np.ascontiguousarray([s for s, _ in runs], dtype=np.int32)
+        lens = np.ascontiguousarray([len(t) for _, t in runs], dtype=np.int32)
+        toks = np.ascontiguousarray([x for _, t in runs for x in t], dtype=np.uint32)
+        i32p, u32p = C.POINTER(C.c_int), C.POINTER(C.c_uint32)
+        if want is None or len(want) == 0:
+            _check(lib().b200_step(self._h, seqs.size, seqs.ctypes.data_as(i32p), lens.ctypes.data_as(i32p), toks.ctypes.data_as(u32p),
+                                   None, 0, None))
+            return None
+        w = np.ascontiguousarray(want, dtype=np.int32)
+        out = np.empty((w.size, self.vocab), dtype=np.float32)
+        _check(lib().b200_step(self._h, seqs.size, seqs.ctypes.data_as(i32p), lens.ctypes.data_as(i32p), toks.ctypes.data_as(u32p),
+                               w.ctypes.data_as(i32p), w.size, _fp(out)))
+        return out
+
+    def layer_runs(self):
+        v = C.c_int(0)
+        _check(lib().b200_ctx_layer_runs(self._h, C.byref(v)))
+        return v.value
+
+    def taps(self, n_tokens):
+        """Residual stream after every layer run for the FIRST run of the last step (taps=True): [layer runs, n_tokens, width]."""
+        out = np.empty((self.layer_runs(), n_tokens, self.desc["hidden"]), dtype=np.float32)
+        _check(lib().b200_get_taps(self._h, _fp(out), out.size))
+        return out
+
+    def pool_counts(self):
+        """(slots that own a cache / state block, blocks waiting in the pool)."""
+        a, b = C.c_int(0), C.c_int(0)
+        _check(lib().b200_ctx_pool_counts(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+
 class GroupInference:
     """GpuInference over the GPUs of ONE process (b200_group_*): tensor parallel for dense models, expert parallel for MoE models,
     one host thread per device inside the library -- the caller never sees ranks (TensorParallel trait,
@@ -855,7 +987,7 @@ class GroupInference:
     def path(self):
         v = C.c_int(0)
         _check(lib().b200_ctx_path(self._ctx(0), C.byref(v)))
-        return ("graph", "mega", "stream", "stream2")[v.value]
+        return ("graph", "mega", "stream", "stream2", "layers")[v.value]
 
     def forward(self, token_id, seq=0):
         logits = np.empty(self.vocab, dtype=np.float32)

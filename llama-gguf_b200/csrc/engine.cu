@@ -15,6 +15,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <chrono>
 #include <cstring>
 #include <algorithm>
 #include <condition_variable>
@@ -42,6 +43,7 @@
 #include "quant.cuh"
 #include "stream.cuh"
 #include "stream2.cuh"
+#include "layerprog.h"
 
 using namespace b200;
 
@@ -247,6 +249,8 @@ struct b200_ctx {
     int* h_err = nullptr;   // pinned copy of the first watchdog word, fetched with every synchronising call
     int* h_token = nullptr;
     std::vector<Slot> slots;
+    // layer-program model (layerprog.cu): when set, every entry point below runs through lp_run(); the slots keep the host positions
+    LpModel* lp = nullptr;
     // options
     bool use_graph = true, use_pdl = true, use_taps = false;
     // statistics
@@ -356,6 +360,95 @@ extern "C" int b200_ctx_create(const b200_model_desc* desc, const b200_parallel_
     c->smem_optin = (size_t)prop.sharedMemPerBlockOptin;
     c->layers.resize(d.n_layers);
     *out = c;
+    return B200_OK;
+}
+
+
+// ------------------------------------------------------------------ layer-program contexts (layerprog.cu)
+// One batch of token runs through a layer-program model: positions come from (and go back to) the slots of the context.
+static int lp_run(b200_ctx* c, const char* fn, int n_runs, const int* seqs, const int* lens, const uint32_t* tokens, const int* want, int n_want,
+                  float* logits_out, uint32_t* pick_out) {
+    if (!c->finalized) return fail(B200_ERR_INVALID_ARGUMENT, std::string(fn) + ": context not finalized");
+    std::vector<int> pos0(std::max(n_runs, 0));
+    for (int i = 0; i < n_runs; i++) {
+        if (!seqs || seqs[i] < 0 || seqs[i] >= (int)c->slots.size()) return fail(B200_ERR_INVALID_ARGUMENT, std::string(fn) + ": bad sequence slot");
+        pos0[i] = (int)c->slots[seqs[i]].host_pos;
+    }
+    std::string err;
+    const int rc = lp_step(c->lp, n_runs, seqs, pos0.data(), lens, tokens, want, n_want, logits_out, pick_out, &err);
+    if (rc) {
+        const size_t at = err.find("b200_step");
+        if (at == 0) err = std::string(fn) + err.substr(9);
+        return fail(rc, err);
+    }
+    for (int i = 0; i < n_runs; i++) c->slots[seqs[i]].host_pos += (uint64_t)lens[i];
+    uint64_t launches = 0;
+    lp_stats(c->lp, &launches, nullptr, nullptr);
+    c->launches = launches;
+    return B200_OK;
+}
+#define NOT_LP(c, fn) \
+    if ((c) && (c)->lp) return fail(B200_ERR_UNSUPPORTED, std::string(fn) + ": not available on a layer-program context")
+
+extern "C" int b200_ctx_create_layers(const b200_program_desc* prog, const b200_layer_desc* layers, int device, b200_ctx** out) {
+    if (!prog || !layers || !out) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_create_layers: null argument");
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) {
+        cudaGetLastError();
+        return fail(B200_ERR_NOT_AVAILABLE, "cuda-b200: no CUDA device (this backend has no CPU fallback)");
+    }
+    if (device < 0 || device >= n_dev) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_create_layers: device ordinal out of range");
+    b200_ctx* c = new b200_ctx();
+    c->par.device = device;
+    c->d.hidden = prog->width;
+    c->d.vocab = prog->vocab;
+    c->d.n_layers = prog->n_layers;
+    c->d.max_seq_len = prog->max_seq_len;
+    c->d.max_batch = prog->max_batch;
+    c->d.norm_eps = prog->norm_eps;
+    c->dg = c->d;
+    c->vocab_l = prog->vocab;
+    c->use_taps = env_int("B200_TAPS", 0) != 0;
+    cudaError_t e = cudaSetDevice(device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete c;
+        return fail(B200_ERR_INITIALIZATION_FAILED, std::string("b200_ctx_create_layers: ") + cudaGetErrorString(e));
+    }
+    std::string err;
+    const int rc = lp_create(prog, layers, device, c->stream, c->use_taps, &c->lp, &err);
+    if (rc) {
+        cudaStreamDestroy(c->stream);
+        delete c;
+        return fail(rc, err);
+    }
+    *out = c;
+    return B200_OK;
+}
+
+extern "C" int b200_step(b200_ctx* c, int n_runs, const int* seqs, const int* lens, const uint32_t* tokens, const int* want_rows, int n_want,
+                         float* logits_out) {
+    if (!c) return fail(B200_ERR_INVALID_ARGUMENT, "b200_step: null ctx");
+    if (!c->lp) return fail(B200_ERR_UNSUPPORTED, "b200_step: only layer-program contexts take batches of token runs");
+    return lp_run(c, "b200_step", n_runs, seqs, lens, tokens, want_rows, logits_out ? n_want : 0, logits_out, nullptr);
+}
+
+extern "C" int b200_ctx_layer_runs(b200_ctx* c, int* out) {
+    if (!c || !out) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_layer_runs: null argument");
+    *out = c->lp ? lp_layer_runs(c->lp) : c->d.n_layers;
+    return B200_OK;
+}
+
+extern "C" int b200_get_taps(b200_ctx* c, float* out, size_t cap_floats) {
+    if (!c || !c->lp) return fail(B200_ERR_UNSUPPORTED, "b200_get_taps: layer-program contexts only (b200_get_hidden elsewhere)");
+    std::string err;
+    const int rc = lp_get_taps(c->lp, out, cap_floats, &err);
+    return rc ? fail(rc, err) : B200_OK;
+}
+
+extern "C" int b200_ctx_pool_counts(b200_ctx* c, int* live, int* pooled) {
+    if (!c || !c->lp) return fail(B200_ERR_UNSUPPORTED, "b200_ctx_pool_counts: layer-program contexts only");
+    lp_pool_counts(c->lp, live, pooled);
     return B200_OK;
 }
 
@@ -474,6 +567,11 @@ static cudaError_t h2d_2d(b200_ctx* c, void* dst, size_t dpitch, const void* src
 extern "C" int b200_ctx_upload_tensor(b200_ctx* c, const char* gguf_name, uint32_t ggml_type, const uint64_t* ne,
                                       int n_dims, const void* host, size_t nbytes) {
     if (!c || !gguf_name || !ne || !host) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_upload_tensor: null argument");
+    if (c->lp) {
+        std::string err;
+        const int rc = lp_upload(c->lp, gguf_name, ggml_type, ne, n_dims, host, nbytes, &err);
+        return rc ? fail(rc, err) : B200_OK;
+    }
     if (c->finalized) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_upload_tensor: context already finalized");
     if (n_dims < 1 || n_dims > 3) return fail(B200_ERR_SHAPE_MISMATCH, std::string(gguf_name) + ": 1..3 dims expected");
     if (!type_supported((int)ggml_type))
@@ -560,6 +658,15 @@ static int check_f32_vec(const DevTensor& t, const char* what, uint64_t n, int l
 extern "C" int b200_ctx_finalize(b200_ctx* c) {
     if (!c) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_finalize: null ctx");
     if (c->finalized) return B200_OK;
+    if (c->lp) {
+        std::string err;
+        const int rc = lp_finalize(c->lp, &err);
+        if (rc) return fail(rc, err);
+        c->slots.resize(c->d.max_batch);
+        lp_stats(c->lp, nullptr, &c->weight_bytes_per_token, nullptr);
+        c->finalized = true;
+        return B200_OK;
+    }
     const b200_model_desc& d = c->d;
     CU(cudaSetDevice(c->par.device));
     const uint64_t H = d.hidden, hd = d.head_dim, nh = d.n_heads, nkv = d.n_kv_heads, I = d.ffn, V = d.vocab;
@@ -728,6 +835,7 @@ static unsigned int* tp_flags(const b200_ctx* c, uint8_t* base) {
 static float* tp_cand(const b200_ctx* c, uint8_t* base) { return reinterpret_cast<float*>(tp_flags(c, base) + 64); }
 
 extern "C" int b200_ctx_tp_handle(b200_ctx* c, void* handle_out64) {
+    NOT_LP(c, "b200_ctx_tp_handle");
     if (!c || !handle_out64) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_tp_handle: null argument");
     CU(cudaSetDevice(c->par.device));
     if (!c->tp_region) {
@@ -745,6 +853,7 @@ extern "C" int b200_ctx_tp_handle(b200_ctx* c, void* handle_out64) {
 }
 
 extern "C" int b200_ctx_tp_set_peer(b200_ctx* c, int peer_rank, const void* handle64) {
+    NOT_LP(c, "b200_ctx_tp_set_peer");
     if (!c || !handle64) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_tp_set_peer: null argument");
     if (peer_rank < 0 || peer_rank >= c->par.world_size) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_tp_set_peer: bad rank");
     if (peer_rank == c->par.rank) return B200_OK;
@@ -762,6 +871,7 @@ extern "C" void b200_ctx_destroy(b200_ctx* c) {
     if (!c) return;
     cudaSetDevice(c->par.device);
     if (c->stream) cudaStreamSynchronize(c->stream);
+    lp_destroy(c->lp);
     if (c->gemv_graph) cudaGraphExecDestroy(c->gemv_graph);
     for (auto& kv : c->tensors)
         if (!kv.second.arena) cudaFree(kv.second.d);
@@ -2080,6 +2190,7 @@ static int flush_pending(b200_ctx* c, int seq) {
 }
 
 extern "C" int b200_ctx_set_kv_format(b200_ctx* c, int format) {
+    NOT_LP(c, "b200_ctx_set_kv_format");
     if (!c) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_set_kv_format: null ctx");
     if (c->finalized) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_set_kv_format: the context is finalized already");
     if (format != 0 && format != 1) return fail(B200_ERR_UNSUPPORTED, "b200_ctx_set_kv_format: 0 = f32, 1 = int8 (FP8 formats of kv_quantized.rs are not built)");
@@ -2111,6 +2222,11 @@ static int spec_enqueue(b200_ctx* c, int seq, int buf) {
 
 extern "C" int b200_forward(b200_ctx* c, int seq, uint32_t token, float* logits_out) {
     int rc;
+    if (c && c->lp) {
+        if (!logits_out) return fail(B200_ERR_INVALID_ARGUMENT, "b200_forward: null logits_out");
+        const int one = 1, row = 0;
+        return lp_run(c, "b200_forward", 1, &seq, &one, &token, &row, 1, logits_out, nullptr);
+    }
     if (c && c->finalized && seq >= 0 && seq < (int)c->slots.size() && c->slots[seq].spec && logits_out) {
         Slot& sl = c->slots[seq];
         const int buf = sl.spec_buf;
@@ -2158,6 +2274,10 @@ extern "C" int b200_forward(b200_ctx* c, int seq, uint32_t token, float* logits_
 
 extern "C" int b200_prefill_token(b200_ctx* c, int seq, uint32_t token) {
     int rc;
+    if (c && c->lp) {
+        const int one = 1;
+        return lp_run(c, "b200_prefill_token", 1, &seq, &one, &token, nullptr, 0, nullptr, nullptr);
+    }
     if ((rc = check_slot(c, seq, "b200_prefill_token"))) return rc;
     if ((rc = check_token(c, seq, token, "b200_prefill_token"))) return rc;
     CU(cudaSetDevice(c->par.device));
@@ -2179,6 +2299,11 @@ extern "C" int b200_prefill_token(b200_ctx* c, int seq, uint32_t token) {
 
 extern "C" int b200_prefill(b200_ctx* c, int seq, const uint32_t* tokens, int n, float* logits_out) {
     int rc;
+    if (c && c->lp) {
+        if (!tokens || n <= 0) return fail(B200_ERR_INVALID_ARGUMENT, "b200_prefill: no tokens");
+        const int row = n - 1;
+        return lp_run(c, "b200_prefill", 1, &seq, &n, tokens, &row, logits_out ? 1 : 0, logits_out, nullptr);
+    }
     if ((rc = check_slot(c, seq, "b200_prefill"))) return rc;
     if (!tokens || n <= 0) return fail(B200_ERR_INVALID_ARGUMENT, "b200_prefill: no tokens");
     if (!c->slots[seq].pending.empty() && (rc = flush_pending(c, seq))) return rc;
@@ -2206,6 +2331,11 @@ extern "C" int b200_prefill(b200_ctx* c, int seq, const uint32_t* tokens, int n,
 
 extern "C" int b200_decode_batch(b200_ctx* c, const int* seqs, const uint32_t* tokens, int n, float* logits_out) {
     if (!c || !seqs || !tokens || !logits_out || n <= 0) return fail(B200_ERR_INVALID_ARGUMENT, "b200_decode_batch: bad argument");
+    if (c->lp) {
+        std::vector<int> ones(n, 1), rows(n);
+        for (int i = 0; i < n; i++) rows[i] = i;
+        return lp_run(c, "b200_decode_batch", n, seqs, ones.data(), tokens, rows.data(), n, logits_out, nullptr);
+    }
     if (c->par.world_size > 1)   // a rank produces vocab / world_size logits per row: the n x vocab layout of this call does not apply
         return fail(B200_ERR_UNSUPPORTED, "b200_decode_batch: not available under tensor parallelism (use b200_forward per sequence)");
     for (int i = 0; i < n; i++)
@@ -2260,6 +2390,12 @@ extern "C" int b200_decode_batch(b200_ctx* c, const int* seqs, const uint32_t* t
 extern "C" int b200_reset(b200_ctx* c, int seq) {
     int rc;
     if ((rc = check_slot(c, seq, "b200_reset"))) return rc;
+    if (c->lp) {   // the slot's cache and state go back to the pool
+        std::string err;
+        if ((rc = lp_release(c->lp, seq, &err))) return fail(rc, err);
+        c->slots[seq].host_pos = 0;
+        return B200_OK;
+    }
     CU(cudaSetDevice(c->par.device));
     Slot& sl = c->slots[seq];
     sl.pending.clear();
@@ -2281,6 +2417,19 @@ extern "C" int b200_decode_greedy(b200_ctx* c, int seq, uint32_t first_token, in
     int rc;
     if ((rc = check_slot(c, seq, "b200_decode_greedy"))) return rc;
     if (n_steps <= 0 || n_steps > kMaxGenerated) return fail(B200_ERR_INVALID_ARGUMENT, "b200_decode_greedy: bad n_steps");
+    if (c->lp) {   // one step per token, the pick made on the device; the time is the host's
+        const auto t0 = std::chrono::steady_clock::now();
+        uint32_t tok = first_token;
+        const int one = 1, row = 0;
+        for (int i = 0; i < n_steps; i++) {
+            uint32_t next = 0;
+            if ((rc = lp_run(c, "b200_decode_greedy", 1, &seq, &one, &tok, &row, 1, nullptr, &next))) return rc;
+            if (tokens_out) tokens_out[i] = next;
+            tok = next;
+        }
+        if (elapsed_ms) *elapsed_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        return B200_OK;
+    }
     if (first_token >= (uint32_t)c->d.vocab) return fail(B200_ERR_INVALID_ARGUMENT, "b200_decode_greedy: token exceeds vocab size");
     if ((rc = flush_pending(c, seq))) return rc;
     Slot& sl = c->slots[seq];
@@ -2502,6 +2651,7 @@ extern "C" int b200_group_ctx(b200_group* g, int rank, b200_ctx** out) {
 extern "C" int b200_get_hidden(b200_ctx* c, int seq, int layer, float* out) {
     int rc;
     if ((rc = check_slot(c, seq, "b200_get_hidden"))) return rc;
+    NOT_LP(c, "b200_get_hidden (use b200_get_taps)");
     if (!c->use_taps) return fail(B200_ERR_UNSUPPORTED, "b200_get_hidden: taps are off (set B200_TAPS=1 before b200_ctx_create)");
     if (layer < 0 || layer > c->d.n_layers || !out) return fail(B200_ERR_INVALID_ARGUMENT, "b200_get_hidden: bad layer");
     CU(cudaSetDevice(c->par.device));
@@ -2513,6 +2663,7 @@ extern "C" int b200_get_hidden(b200_ctx* c, int seq, int layer, float* out) {
 // Debug: globaltimer stamps (ns) of CTA 0 after the embedding barrier and after every phase barrier of the last
 // token run by the megakernel.  First call arms the stamps; returns the number of values written to out.
 extern "C" int b200_debug_mega_timeline(b200_ctx* c, unsigned long long* out, int max_n) {
+    NOT_LP(c, "b200_debug_mega_timeline");
     if (!c || !c->mega_ok) return 0;
     cudaSetDevice(c->par.device);
     const int n = (c->stream2_ok ? c->s2_phases : c->mega_phases) + 1;
@@ -2530,6 +2681,7 @@ extern "C" int b200_debug_mega_timeline(b200_ctx* c, unsigned long long* out, in
 // Debug: per-warp globaltimer stamps (gemv_mma.cuh MMA_STAMP) of one GEMV phase of slot 0's megakernel program.
 // phase >= 0 arms (patches the phase descriptor); phase < 0 fetches grid*16*8 values into out.
 extern "C" int b200_debug_mega_phase(b200_ctx* c, int phase, unsigned long long* out, int max_n) {
+    NOT_LP(c, "b200_debug_mega_phase");
     if (!c || !c->mega_ok) return 0;
     cudaSetDevice(c->par.device);
     static unsigned long long* buf = nullptr;
@@ -2554,6 +2706,7 @@ extern "C" int b200_debug_mega_phase(b200_ctx* c, int phase, unsigned long long*
 
 // Debug: copy one of the activation buffers to the host (0 xa, 1 xb, 2 qkv, 3 attn, 4 hbuf, 5 logits).
 extern "C" int b200_debug_read(b200_ctx* c, int which, float* out, int n) {
+    NOT_LP(c, "b200_debug_read");
     if (!c || !out) return 0;
     cudaSetDevice(c->par.device);
     cudaStreamSynchronize(c->stream);
@@ -2564,6 +2717,10 @@ extern "C" int b200_debug_read(b200_ctx* c, int which, float* out, int n) {
 
 extern "C" int b200_ctx_stats(b200_ctx* c, uint64_t* kernel_launches, uint64_t* weight_bytes, uint64_t* kv_bytes_per_pos) {
     if (!c) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_stats: null ctx");
+    if (c->lp) {
+        lp_stats(c->lp, kernel_launches, weight_bytes, kv_bytes_per_pos);
+        return B200_OK;
+    }
     if (kernel_launches) *kernel_launches = c->launches;
     if (weight_bytes) *weight_bytes = c->weight_bytes_per_token;
     if (kv_bytes_per_pos)   // f32 rows, or int8 rows + one f32 scale each
@@ -2575,13 +2732,17 @@ extern "C" int b200_ctx_stats(b200_ctx* c, uint64_t* kernel_launches, uint64_t* 
 // 2 = streamed megakernel (stream.cuh), 3 = second streamed megakernel (stream2.cuh).
 extern "C" int b200_ctx_path(b200_ctx* c, int* out) {
     if (!c || !out) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_path: null argument");
-    *out = c->mega_ok ? (c->stream2_ok ? 3 : c->stream_ok ? 2 : 1) : 0;
+    *out = c->lp ? 4 : c->mega_ok ? (c->stream2_ok ? 3 : c->stream_ok ? 2 : 1) : 0;
     return B200_OK;
 }
 
 // Debug: the watchdog words of the tensor-pipe / megakernel paths (0 = no wait ever gave up); clears them.
 extern "C" int b200_debug_err(b200_ctx* c, int* out8) {
     if (!c || !out8) return fail(B200_ERR_INVALID_ARGUMENT, "b200_debug_err: null argument");
+    if (c->lp) {   // (no bounded waits on this path)
+        memset(out8, 0, 8 * sizeof(int));
+        return B200_OK;
+    }
     CU(cudaSetDevice(c->par.device));
     CU(cudaStreamSynchronize(c->stream));
     CU(cudaMemcpy(out8, c->mma_err, 8 * sizeof(int), cudaMemcpyDeviceToHost));
@@ -2595,6 +2756,7 @@ extern "C" int b200_debug_err(b200_ctx* c, int* out8) {
 // argmax launches left out) `iters` times between two CUDA events on the launching stream.
 extern "C" int b200_bench_gemv_pass(b200_ctx* c, int seq, int iters, float* avg_ms_per_pass, uint64_t* launches_per_pass,
                                     uint64_t* bytes_per_pass) {
+    NOT_LP(c, "b200_bench_gemv_pass");
     int rc;
     if ((rc = check_slot(c, seq, "b200_bench_gemv_pass"))) return rc;
     if (iters <= 0) return fail(B200_ERR_INVALID_ARGUMENT, "b200_bench_gemv_pass: iters <= 0");
@@ -2639,6 +2801,7 @@ extern "C" int b200_bench_gemv_pass(b200_ctx* c, int seq, int iters, float* avg_
 // "%d" walks every layer's tensor in order (footprint >> L2, the decode access pattern);
 // a plain name times one tensor and writes a 256 MB buffer between launches to flush L2.
 extern "C" int b200_bench_weight_gemv(b200_ctx* c, const char* gguf_name, int iters, float* avg_ms, uint64_t* bytes) {
+    NOT_LP(c, "b200_bench_weight_gemv");
     if (!c || !c->finalized || !gguf_name || iters <= 0) return fail(B200_ERR_INVALID_ARGUMENT, "b200_bench_weight_gemv: bad argument");
     CU(cudaSetDevice(c->par.device));
     std::vector<const DevTensor*> ts;
@@ -3258,6 +3421,7 @@ static cudaError_t stage_end(b200_ctx* c) {
 // tensors it does not use (rope_freqs.weight, tokenizer tables ...) are skipped and counted.  B200_LOAD_STAGED=0 falls back to
 // cudaMemcpy straight from the mapping (pageable: the driver stages it internally, one thread) for comparison.
 extern "C" int b200_ctx_load_gguf(b200_ctx* c, b200_gguf* g, b200_load_stats* stats) {
+    NOT_LP(c, "b200_ctx_load_gguf");
     if (!c || !g) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_load_gguf: null argument");
     if (c->finalized) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_load_gguf: context already finalized");
     CU(cudaSetDevice(c->par.device));
@@ -3374,6 +3538,11 @@ static bool batch_gemm_eligible(b200_ctx* c, int n) {
 // of n x vocab logits (16 MB per step at batch 32 on Llama-3).  Same two paths as b200_decode_batch.
 extern "C" int b200_decode_batch_greedy(b200_ctx* c, const int* seqs, const uint32_t* tokens, int n, uint32_t* next_out) {
     if (!c || !seqs || !tokens || !next_out || n <= 0) return fail(B200_ERR_INVALID_ARGUMENT, "b200_decode_batch_greedy: bad argument");
+    if (c->lp) {
+        std::vector<int> ones(n, 1), rows(n);
+        for (int i = 0; i < n; i++) rows[i] = i;
+        return lp_run(c, "b200_decode_batch_greedy", n, seqs, ones.data(), tokens, rows.data(), n, nullptr, next_out);
+    }
     if (c->par.world_size > 1) return fail(B200_ERR_UNSUPPORTED, "b200_decode_batch_greedy: not available under tensor parallelism");
     for (int i = 0; i < n; i++)
         for (int j = 0; j < i; j++)
@@ -3546,7 +3715,7 @@ extern "C" int b200_batch_step(b200_batch* b, b200_batch_event* out, int cap, in
         BatchSeq& s = b->active[i];
         const int rc = b200_reset(c, s.slot);
         if (rc) { action[i] = 3; err[i] = g_err; continue; }
-        if ((int)s.tokens.size() >= c->prefill_gemm_min && prefill_gemm_ok(c, true)) long_idx.push_back((int)i);
+        if (c->lp || ((int)s.tokens.size() >= c->prefill_gemm_min && prefill_gemm_ok(c, true))) long_idx.push_back((int)i);
         else { short_idx.push_back((int)i); max_short = std::max(max_short, s.tokens.size()); }
     }
     const size_t n_sub = std::max<size_t>(max_short, dec_idx.empty() ? 0 : 1);
@@ -3635,6 +3804,7 @@ extern "C" const char* b200_batch_last_error(b200_batch* b) { return b ? b->last
 
 // ------------------------------------------------------------------ greedy continuation + lab positioning
 extern "C" int b200_ctx_set_speculation(b200_ctx* c, int on) {
+    NOT_LP(c, "b200_ctx_set_speculation");
     if (!c) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_set_speculation: null ctx");
     if (!c->finalized) return fail(B200_ERR_INVALID_ARGUMENT, "b200_ctx_set_speculation: finalize the context first");
     for (int s = 0; s < (int)c->slots.size(); s++) {
@@ -3661,6 +3831,7 @@ extern "C" int b200_ctx_speculation_stats(b200_ctx* c, int* enabled, uint64_t* h
 }
 // Lab: declare the first `pos` positions of the slot's KV cache valid as they are (timing attention at depth without a prompt).
 extern "C" int b200_debug_set_position(b200_ctx* c, int seq, uint64_t pos) {
+    NOT_LP(c, "b200_debug_set_position");
     int rc;
     if ((rc = check_slot(c, seq, "b200_debug_set_position"))) return rc;
     if (pos >= (uint64_t)c->d.max_seq_len) return fail(B200_ERR_INVALID_ARGUMENT, "b200_debug_set_position: beyond the context");

@@ -1,0 +1,1272 @@
+// layerprog.cu — layer-program models: a decoder given as a list of layers, each with its own token mixer (see the block
+// "layer-program models" of include/llama_b200.h for the mechanisms and their parameters).
+//
+// A STEP is a batch of token runs, each continuing one sequence slot.  All rows of a step share the weight passes (one GEMM per
+// fused projection over all rows); the mixers work per (run, head) from the slot's cache / state, so a prompt, a portion of a
+// prompt and a single decoded token are the same code with another run length.  Row r of a step knows its run and its position
+// through small device arrays written once per step.
+//
+// Precision: the residual stream, norms, softmax, gates, decays, unit norms and every recurrent state are f32 in both compute
+// modes.  B200_COMPUTE_BF16 keeps the matrices and the GEMM operands in bf16 (f32 accumulation, f32 results);
+// B200_COMPUTE_F32 keeps them in f32 and multiplies with FMA on the CUDA cores (no reduced-precision matrix mode).
+#include "layerprog.h"
+
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <vector>
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+// ------------------------------------------------------------------------------------------------ device helpers
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float wmax(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float logsigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
+
+// Per-step row / run tables (device).  Row r belongs to run row_run[r] and sits at position row_pos[r] of its sequence; run s covers
+// rows [run_start[s], run_start[s + 1]), starts at position run_pos0[s] and owns the cache run_kv[s] and the state run_rec[s].
+struct StepMeta {
+    const int* tok;
+    const int* row_run;
+    const int* row_pos;
+    const int* run_start;
+    const int* run_pos0;
+    uint8_t* const* run_kv;
+    uint8_t* const* run_rec;
+    const int* want;
+};
+
+// ------------------------------------------------------------------------------------------------ embedding
+// x[r] = table[token] * scale (+ sinusoidal position vector: entry 2i = sin(p w_i), entry 2i + 1 = cos(p w_i), w_i = 10000^(-2i/width)).
+// The angle and its sine are evaluated in double: at positions in the thousands an f32 angle alone is off by 1e-4.
+template <typename T>
+__global__ void lp_embed_kernel(StepMeta sm, const T* __restrict__ table, const double* __restrict__ inv_freq, float* __restrict__ x,
+                                int width, float scale, int sinusoid) {
+    const int r = blockIdx.x;
+    const T* row = table + (size_t)sm.tok[r] * width;
+    const double p = (double)sm.row_pos[r];
+    for (int i = threadIdx.x; i < (width + 1) / 2; i += blockDim.x) {
+        float s = 0.0f, c = 0.0f;
+        if (sinusoid) {
+            double ds, dc;
+            sincos(p * inv_freq[i], &ds, &dc);
+            s = (float)ds;
+            c = (float)dc;
+        }
+        x[(size_t)r * width + 2 * i] = to_f(row[2 * i]) * scale + s;
+        if (2 * i + 1 < width) x[(size_t)r * width + 2 * i + 1] = to_f(row[2 * i + 1]) * scale + c;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ RMS norm
+// out[b] = x[src] / sqrt(mean(x[src]^2) + eps) * w, src = gather ? gather[b] : b.  add != null: x[src] += add first (stored back):
+// the per-pass step vector of a repeated layer range.  One block per row.
+template <typename OutT>
+__global__ void lp_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float* __restrict__ w, OutT* __restrict__ out,
+                                  const int* __restrict__ gather, int width, float eps) {
+    const int b = blockIdx.x;
+    const int r = gather ? gather[b] : b;
+    float* xr = x + (size_t)r * width;
+    __shared__ float red[33];
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = xr[c];
+        if (add) {
+            v += add[c];
+            xr[c] = v;
+        }
+        ss += v * v;
+    }
+    ss = wsum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+        t = wsum(t);
+        if (threadIdx.x == 0) red[32] = 1.0f / sqrtf(t / (float)width + eps);
+    }
+    __syncthreads();
+    const float inv = red[32];
+    for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)b * width + c] = from_f<OutT>(xr[c] * inv * w[c]);
+}
+
+// ------------------------------------------------------------------------------------------------ GEMM (CUDA cores)
+// Y[r][n] = epi(alpha * sum_k X[r][k] * W[n][k]); products of the stored operand values in f32, f32 accumulation.
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_RELU2 = 2 };
+template <typename T, int EPI>
+__device__ __forceinline__ void epi_store(void* Y, size_t idx, float v) {
+    if (EPI == EPI_STORE) reinterpret_cast<float*>(Y)[idx] = v;
+    else if (EPI == EPI_ADD) reinterpret_cast<float*>(Y)[idx] += v;
+    else {
+        const float z = fmaxf(v, 0.0f);
+        reinterpret_cast<T*>(Y)[idx] = from_f<T>(z * z);
+    }
+}
+
+constexpr int GB = 64, GK = 16;
+template <typename T, int EPI>
+__global__ void __launch_bounds__(256) lp_gemm_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int ldw, void* __restrict__ Y,
+                                                      int ldy, int R, int N, int K, float alpha) {
+    __shared__ float As[GK][GB + 4];
+    __shared__ float Bs[GK][GB + 4];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int r0 = blockIdx.y * GB, n0 = blockIdx.x * GB;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += GK) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int k = k0 + lk + i;
+            const int r = r0 + lr, n = n0 + lr;
+            As[lk + i][lr] = (r < R && k < K) ? to_f(X[(size_t)r * ldx + k]) : 0.0f;
+            Bs[lk + i][lr] = (n < N && k < K) ? to_f(W[(size_t)n * ldw + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GK; k++) {
+            const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+            const float4 b = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = r0 + ty * 4 + i;
+        if (r >= R) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) epi_store<T, EPI>(Y, (size_t)r * ldy + n, alpha * acc[i][j]);
+        }
+    }
+}
+
+// Few rows (decoding): one warp per output column, the weight row is read once with 16-byte loads and meets up to GV_ROWS
+// activation rows; W streams from HBM at the copy rate, the activations come out of L1/L2.
+constexpr int GV_ROWS = 8;
+template <typename T> struct Vec8;
+template <> struct Vec8<bf16> {
+    static constexpr int N = 8;
+    __device__ static void load(const bf16* p, float* o) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            o[2 * i] = __uint_as_float(w[i] << 16);
+            o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+template <> struct Vec8<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float* o) {
+        const float4 u = *reinterpret_cast<const float4*>(p);
+        o[0] = u.x; o[1] = u.y; o[2] = u.z; o[3] = u.w;
+    }
+};
+template <typename T, int EPI>
+__global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int ldw, void* __restrict__ Y,
+                                                      int ldy, int R, int N, int K, float alpha, int vec_ok) {
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (n >= N) return;
+    constexpr int VN = Vec8<T>::N;
+    const T* wr = W + (size_t)n * ldw;
+    for (int rb = 0; rb < R; rb += GV_ROWS) {
+        const int nr = min(GV_ROWS, R - rb);
+        float acc[GV_ROWS] = {};
+        if (vec_ok) {
+            for (int k = lane * VN; k < K; k += 32 * VN) {
+                float wv[VN], xv[VN];
+                Vec8<T>::load(wr + k, wv);
+#pragma unroll
+                for (int i = 0; i < GV_ROWS; i++) {
+                    if (i < nr) {
+                        Vec8<T>::load(X + (size_t)(rb + i) * ldx + k, xv);
+#pragma unroll
+                        for (int e = 0; e < VN; e++) acc[i] = fmaf(wv[e], xv[e], acc[i]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) {
+                const float wv = to_f(wr[k]);
+#pragma unroll
+                for (int i = 0; i < GV_ROWS; i++)
+                    if (i < nr) acc[i] = fmaf(wv, to_f(X[(size_t)(rb + i) * ldx + k]), acc[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < GV_ROWS; i++) {
+            if (i < nr) {
+                const float s = wsum(acc[i]);
+                if (lane == 0) epi_store<T, EPI>(Y, (size_t)(rb + i) * ldy + n, alpha * s);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ windowed attention
+// After the fused projection P[r] = [q | k | v | gate | ...]: per-head RMS norm of q and k (shared weight of size dim), q to qbuf,
+// k and v to the run's cache rows at the row's position.  Cache of a run: K [cap][G * dim] then V [cap][G * vdim], f32.
+struct AttnGeom {
+    int H, G, dim, vdim, window, keep_first, qk_norm, out_gate;
+    float scale, eps;
+    int q_off, k_off, v_off, g_off;   // columns of P
+    size_t kv_off;                    // byte offset of this layer run inside a slot's cache block
+    int cap;                          // positions a slot's cache holds
+};
+__global__ void lp_attn_prep_kernel(StepMeta sm, AttnGeom a, const float* __restrict__ P, int ldp, const float* __restrict__ qw,
+                                    const float* __restrict__ kw, float* __restrict__ qbuf) {
+    const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int run = sm.row_run[r], pos = sm.row_pos[r];
+    const float* p = P + (size_t)r * ldp;
+    float* kc = reinterpret_cast<float*>(sm.run_kv[run] + a.kv_off) + (size_t)pos * a.G * a.dim;
+    float* vc = reinterpret_cast<float*>(sm.run_kv[run] + a.kv_off) + (size_t)a.cap * a.G * a.dim + (size_t)pos * a.G * a.vdim;
+    for (int h = warp; h < a.H + a.G; h += nw) {
+        const bool isq = h < a.H;
+        const float* src = isq ? p + a.q_off + h * a.dim : p + a.k_off + (h - a.H) * a.dim;
+        float* dst = isq ? qbuf + (size_t)r * a.H * a.dim + h * a.dim : kc + (h - a.H) * a.dim;
+        const float* w = isq ? qw : kw;
+        float inv = 1.0f;
+        if (a.qk_norm) {
+            float ss = 0.0f;
+            for (int d = lane; d < a.dim; d += 32) ss += src[d] * src[d];
+            ss = wsum(ss);
+            inv = 1.0f / sqrtf(ss / (float)a.dim + a.eps);
+        }
+        for (int d = lane; d < a.dim; d += 32) dst[d] = a.qk_norm ? src[d] * inv * w[d] : src[d];
+    }
+    for (int c = threadIdx.x; c < a.G * a.vdim; c += blockDim.x) vc[c] = p[a.v_off + c];
+}
+
+// One warp per (row, query head): keys in blocks of 32, one key per lane for the scores (q from shared memory), online softmax in
+// f32, then the 32 value rows are added lane-per-channel.  Visible keys of position i: [0, min(keep_first, lo)) and [lo, i],
+// lo = max(0, i - window + 1).  The output is multiplied by sigmoid(gate) when the layer has an output gate.
+constexpr int ATT_ACC = 16;   // value channels per lane: vdim <= 512
+template <typename OutT>
+__global__ void __launch_bounds__(128) lp_window_attn_kernel(StepMeta sm, AttnGeom a, const float* __restrict__ qbuf, const float* __restrict__ P,
+                                                             int ldp, OutT* __restrict__ out) {
+    extern __shared__ float smem[];
+    const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * (blockDim.x >> 5) + warp;
+    if (h >= a.H) return;
+    float* qs = smem + warp * a.dim;
+    const int run = sm.row_run[r], i = sm.row_pos[r];
+    const int g = h / (a.H / a.G);
+    const float* q = qbuf + (size_t)r * a.H * a.dim + h * a.dim;
+    for (int d = lane; d < a.dim; d += 32) qs[d] = q[d];
+    __syncwarp();
+    const float* kc = reinterpret_cast<const float*>(sm.run_kv[run] + a.kv_off);
+    const float* vc = kc + (size_t)a.cap * a.G * a.dim;
+    const int ldk = a.G * a.dim, ldv = a.G * a.vdim;
+    const int lo = max(0, i - a.window + 1);
+    const int a_end = min(a.keep_first, lo);
+    float m = -INFINITY, l = 0.0f;
+    float acc[ATT_ACC];
+#pragma unroll
+    for (int c = 0; c < ATT_ACC; c++) acc[c] = 0.0f;
+    const bool v4 = (a.dim & 3) == 0;
+    for (int part = 0; part < 2; part++) {
+        const int beg = part ? lo : 0, end = part ? i + 1 : a_end;
+        for (int j0 = beg; j0 < end; j0 += 32) {
+            const int j = j0 + lane;
+            float s = -INFINITY;
+            if (j < end) {
+                const float* kr = kc + (size_t)j * ldk + g * a.dim;
+                float d0 = 0.0f;
+                if (v4) {
+                    for (int d = 0; d < a.dim; d += 4) {
+                        const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+                        d0 = fmaf(qs[d], kv.x, d0);
+                        d0 = fmaf(qs[d + 1], kv.y, d0);
+                        d0 = fmaf(qs[d + 2], kv.z, d0);
+                        d0 = fmaf(qs[d + 3], kv.w, d0);
+                    }
+                } else {
+                    for (int d = 0; d < a.dim; d++) d0 = fmaf(qs[d], kr[d], d0);
+                }
+                s = d0 * a.scale;
+            }
+            const float m_new = fmaxf(m, wmax(s));
+            const float p = j < end ? expf(s - m_new) : 0.0f;
+            const float corr = expf(m - m_new);      // (m = -inf on the first block: 0)
+            l = l * corr + wsum(p);
+            m = m_new;
+#pragma unroll
+            for (int c = 0; c < ATT_ACC; c++) acc[c] *= corr;
+            const int cnt = min(32, end - j0);
+            for (int jj = 0; jj < cnt; jj++) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const float* vr = vc + (size_t)(j0 + jj) * ldv + g * a.vdim;
+#pragma unroll
+                for (int c = 0; c < ATT_ACC; c++) {
+                    const int ch = c * 32 + lane;
+                    if (ch < a.vdim) acc[c] = fmaf(pj, vr[ch], acc[c]);
+                }
+            }
+        }
+    }
+    const float invl = 1.0f / l;
+    const float* gate = P + (size_t)r * ldp + a.g_off + h * a.vdim;
+#pragma unroll
+    for (int c = 0; c < ATT_ACC; c++) {
+        const int ch = c * 32 + lane;
+        if (ch < a.vdim) {
+            float o = acc[c] * invl;
+            if (a.out_gate) o *= sigmoid_f(gate[ch]);
+            out[(size_t)r * a.H * a.vdim + h * a.vdim + ch] = from_f<OutT>(o);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ matrix memory
+// Per (run, head): S [dim][vdim], n [dim], m; thread = value channel j, its column S[:, j] lives in registers for the whole run.
+//   i = cap tanh((zi + bi) / cap),  f = logsigmoid(cap tanh((zf + bf) / cap)),  m' = max(f + m, i)
+//   S <- e^(f + m - m') S + e^(i - m') k v^T,  n likewise with k,  o = S^T q / (max(|n . q|, e^(-m')) + 1e-6),  q = (W_q h) dim^(-1/2)
+// State block of a run: S [H][dim][vdim] | n [H][dim] | m [H], f32.
+struct MemGeom {
+    int H, dim, vdim;
+    float cap;
+    int q_off, k_off, v_off, i_off, f_off;
+    size_t rec_off;
+};
+constexpr int SCAN_BD = 64;
+template <int DMAX>
+__global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, MemGeom g, const float* __restrict__ P, int ldp,
+                                                                   const float* __restrict__ ib, const float* __restrict__ fb,
+                                                                   float* __restrict__ O, int ldo) {
+    __shared__ float qs[2][DMAX], ks[2][DMAX], ns[DMAX];
+    const int j = blockIdx.x * SCAN_BD + threadIdx.x, h = blockIdx.y, run = blockIdx.z;
+    const int lane = threadIdx.x & 31;
+    const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
+    float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
+    float* ng = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim + (size_t)h * g.dim;
+    float* mg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim + (size_t)g.H * g.dim + h;
+    const bool live = j < g.vdim;
+    float s[DMAX];
+#pragma unroll
+    for (int d = 0; d < DMAX; d++) s[d] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
+    for (int d = threadIdx.x; d < DMAX; d += SCAN_BD) {
+        ns[d] = d < g.dim ? ng[d] : 0.0f;
+        qs[0][d] = qs[1][d] = ks[0][d] = ks[1][d] = 0.0f;
+    }
+    float m = *mg;
+    const float qscale = 1.0f / sqrtf((float)g.dim);
+    const float bi = ib[h], bf_ = fb[h];
+    __syncthreads();
+    for (int r = r0; r < r1; r++) {
+        const int b = (r - r0) & 1;
+        const float* p = P + (size_t)r * ldp;
+        for (int d = threadIdx.x; d < g.dim; d += SCAN_BD) {
+            qs[b][d] = p[g.q_off + h * g.dim + d] * qscale;
+            ks[b][d] = p[g.k_off + h * g.dim + d];
+        }
+        const float il = g.cap * tanhf((p[g.i_off + h] + bi) / g.cap);
+        const float fl = logsigmoid_f(g.cap * tanhf((p[g.f_off + h] + bf_) / g.cap));
+        const float v = live ? p[g.v_off + h * g.vdim + j] : 0.0f;
+        const float m_new = fmaxf(fl + m, il);
+        const float fa = expf(fl + m - m_new), ia = expf(il - m_new);
+        m = m_new;
+        __syncthreads();                                   // q, k of this token are in place; everyone is done with token r - 1
+        for (int d = threadIdx.x; d < g.dim; d += SCAN_BD) ns[d] = fa * ns[d] + ia * ks[b][d];
+        float acc = 0.0f;
+        const float iv = ia * v;
+#pragma unroll
+        for (int d = 0; d < DMAX; d++) {
+            s[d] = fmaf(fa, s[d], ks[b][d] * iv);
+            acc = fmaf(s[d], qs[b][d], acc);
+        }
+        __syncthreads();                                   // n of this token is in place
+        float nq = 0.0f;
+        for (int d = lane; d < g.dim; d += 32) nq = fmaf(ns[d], qs[b][d], nq);
+        nq = wsum(nq);
+        if (live) O[(size_t)r * ldo + h * g.vdim + j] = acc / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+    }
+    __syncthreads();
+    if (live)
+#pragma unroll
+        for (int d = 0; d < DMAX; d++)
+            if (d < g.dim) Sg[(size_t)d * g.vdim + j] = s[d];
+    if (blockIdx.x == 0) {
+        for (int d = threadIdx.x; d < g.dim; d += SCAN_BD) ng[d] = ns[d];
+        if (threadIdx.x == 0) *mg = m;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ gated delta rule
+// Causal depthwise convolution + SiLU over the first C columns of P (q | k | v of the fused projection).  Weights [C][taps], the last
+// tap meets the current token; inputs before a run's first row come from the run's tail (the last taps - 1 inputs, zero at the
+// start of a sequence).  State block of a run: S [H][dim][vdim] | tail [taps - 1][C], f32.
+struct DeltaGeom {
+    int H, G, dim, vdim, taps, C;     // C = 2 G dim + H vdim
+    int g_off, b_off, a_off;          // columns of P: gate | write strength | decay
+    size_t rec_off;
+    float eps;
+};
+__global__ void lp_conv_silu_kernel(StepMeta sm, DeltaGeom g, const float* __restrict__ P, int ldp, const float* __restrict__ cw,
+                                    float* __restrict__ out) {
+    const int r = blockIdx.x, run = sm.row_run[r];
+    const int t = r - sm.run_start[run];
+    const float* tail = reinterpret_cast<const float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim;
+    for (int c = threadIdx.x; c < g.C; c += blockDim.x) {
+        float y = 0.0f;
+        for (int i = 0; i < g.taps; i++) {
+            const int tt = t - (g.taps - 1) + i;
+            const float in = tt >= 0 ? P[(size_t)(r - t + tt) * ldp + c] : tail[(size_t)(g.taps - 1 + tt) * g.C + c];
+            y = fmaf(cw[(size_t)c * g.taps + i], in, y);
+        }
+        out[(size_t)r * g.C + c] = y * sigmoid_f(y);
+    }
+}
+// After the convolution: the run's tail becomes the last taps - 1 inputs of (old tail ++ new rows).
+__global__ void lp_conv_tail_kernel(StepMeta sm, DeltaGeom g, const float* __restrict__ P, int ldp) {
+    const int run = blockIdx.x, r0 = sm.run_start[run], len = sm.run_start[run + 1] - r0;
+    float* tail = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim;
+    for (int c = threadIdx.x; c < g.C; c += blockDim.x)
+        for (int i = 0; i < g.taps - 1; i++) {
+            const int st = len + i - (g.taps - 1);
+            tail[(size_t)i * g.C + c] = st >= 0 ? P[(size_t)(r0 + st) * ldp + c] : tail[(size_t)(i + len) * g.C + c];
+        }
+}
+// Per (run, head): thread = value channel j with S[:, j] in registers.  q, k become unit vectors (x / sqrt(sum x^2 + 1e-6), q also
+// times dim^(-1/2)); beta = sigmoid(zb); decay = exp(-exp(A_log) softplus(za + dt_bias));
+//   S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q   (the read-out sees this token's write).
+template <int DMAX>
+__global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, DeltaGeom g, const float* __restrict__ QKV, const float* __restrict__ P,
+                                                                 int ldp, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                                 float* __restrict__ O, int ldo) {
+    __shared__ float qs[2][DMAX], ks[2][DMAX];
+    const int j = blockIdx.x * SCAN_BD + threadIdx.x, h = blockIdx.y, run = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hk = h / (g.H / g.G);
+    const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
+    float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
+    const bool live = j < g.vdim;
+    float s[DMAX];
+#pragma unroll
+    for (int d = 0; d < DMAX; d++) s[d] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
+    for (int d = threadIdx.x; d < DMAX; d += SCAN_BD) qs[0][d] = qs[1][d] = ks[0][d] = ks[1][d] = 0.0f;
+    const float rate = expf(A_log[h]), dtb = dt_bias[h];
+    const float qscale = 1.0f / sqrtf((float)g.dim);
+    const int k_col = g.G * g.dim, v_col = 2 * g.G * g.dim;
+    __syncthreads();
+    for (int r = r0; r < r1; r++) {
+        const int b = (r - r0) & 1;
+        const float* x = QKV + (size_t)r * g.C;
+        if (warp < 2) {   // warp 0: q, warp 1: k
+            const float* src = x + (warp ? k_col : 0) + hk * g.dim;
+            float ss = 0.0f;
+            for (int d = lane; d < g.dim; d += 32) ss += src[d] * src[d];
+            ss = wsum(ss);
+            const float inv = (warp ? 1.0f : qscale) / sqrtf(ss + 1e-6f);
+            float* dst = warp ? ks[b] : qs[b];
+            for (int d = lane; d < g.dim; d += 32) dst[d] = src[d] * inv;
+        }
+        const float* p = P + (size_t)r * ldp;
+        const float beta = sigmoid_f(p[g.b_off + h]);
+        const float decay = expf(-rate * softplus_f(p[g.a_off + h] + dtb));
+        const float v = live ? x[v_col + h * g.vdim + j] : 0.0f;
+        __syncthreads();
+        float kd = 0.0f;
+#pragma unroll
+        for (int d = 0; d < DMAX; d++) {
+            s[d] *= decay;
+            kd = fmaf(s[d], ks[b][d], kd);
+        }
+        const float u = beta * (v - kd);
+        float acc = 0.0f;
+#pragma unroll
+        for (int d = 0; d < DMAX; d++) {
+            s[d] = fmaf(ks[b][d], u, s[d]);
+            acc = fmaf(s[d], qs[b][d], acc);
+        }
+        if (live) O[(size_t)r * ldo + h * g.vdim + j] = acc;
+    }
+    if (live)
+#pragma unroll
+        for (int d = 0; d < DMAX; d++)
+            if (d < g.dim) Sg[(size_t)d * g.vdim + j] = s[d];
+}
+
+// out[r][h][c] = o / sqrt(mean_c o^2 + eps) * w[w_per_head ? c : h * vdim + c] * act(gate), act = sigmoid (0) or SiLU (1); one warp
+// per (row, head).  The result is the input of the mixer's output projection.
+template <typename OutT>
+__global__ void lp_headnorm_gate_kernel(const float* __restrict__ O, int ldo, const float* __restrict__ P, int ldp, int g_off,
+                                        const float* __restrict__ w, int w_per_head, int H, int vdim, float eps, int act,
+                                        OutT* __restrict__ out, int R) {
+    const int r = blockIdx.x, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (h >= H || r >= R) return;
+    const float* o = O + (size_t)r * ldo + h * vdim;
+    float ss = 0.0f;
+    for (int c = lane; c < vdim; c += 32) ss += o[c] * o[c];
+    ss = wsum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    const float* gate = P + (size_t)r * ldp + g_off + h * vdim;
+    for (int c = lane; c < vdim; c += 32) {
+        const float z = gate[c];
+        const float ga = act ? z * sigmoid_f(z) : sigmoid_f(z);
+        out[(size_t)r * H * vdim + h * vdim + c] = from_f<OutT>(o[c] * inv * w[w_per_head ? c : h * vdim + c] * ga);
+    }
+}
+
+// Greedy pick per row, the LAST maximum wins (the rule of the library's other paths).
+__global__ void lp_argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    float best = -INFINITY;
+    int bi = 0;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+        if (row[i] >= best) { best = row[i]; bi = i; }
+    __shared__ float sv[1024];
+    __shared__ int si[1024];
+    sv[threadIdx.x] = best;
+    si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int o = blockDim.x >> 1; o > 0; o >>= 1) {
+        if (threadIdx.x < o) {
+            const float v2 = sv[threadIdx.x + o];
+            const int i2 = si[threadIdx.x + o];
+            if (v2 > sv[threadIdx.x] || (v2 == sv[threadIdx.x] && i2 > si[threadIdx.x])) { sv[threadIdx.x] = v2; si[threadIdx.x] = i2; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = si[0];
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+struct Tensor {
+    void* d = nullptr;      // matrices: compute type; vectors: f32
+    bool matrix = false;
+    uint64_t rows = 0, cols = 0;
+    size_t bytes = 0;
+};
+
+struct LayerPlan {
+    b200_layer_desc d{};
+    // fused input projection of the mixer and its column map
+    void* w_in = nullptr;
+    int n_in = 0;
+    AttnGeom ag{};
+    MemGeom mg{};
+    DeltaGeom dg{};
+    const float *norm1 = nullptr, *norm2 = nullptr, *qn = nullptr, *kn = nullptr, *mem_norm = nullptr, *ib = nullptr, *fb = nullptr;
+    const float *conv_w = nullptr, *A_log = nullptr, *dt_bias = nullptr, *delta_norm = nullptr;
+    void *wo_attn = nullptr, *wo_mem = nullptr, *wo_delta = nullptr, *w_up = nullptr, *w_down = nullptr;
+    size_t kv_bytes = 0, rec_bytes = 0;   // per run, per slot (kv_bytes for `cap` positions)
+};
+
+struct SlotMem {
+    uint8_t* kv = nullptr;
+    uint8_t* rec = nullptr;
+};
+
+}  // namespace
+
+struct LpModel {
+    b200_program_desc p{};
+    std::vector<b200_layer_desc> layers;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool f32 = false, taps_on = false, finalized = false;
+    std::map<std::string, Tensor> tensors;
+    std::vector<LayerPlan> plan;        // per layer
+    std::vector<int> runs;              // layer index of every layer run
+    std::vector<int> run_pass;          // pass number t when the run is the first of a pass (step vector t is added), else -1
+    std::vector<size_t> run_kv_off, run_rec_off;
+    size_t slot_kv_bytes = 0, slot_rec_bytes = 0;
+    std::vector<SlotMem> slot;          // per sequence slot; null = holds nothing
+    std::vector<SlotMem> pool;
+    double* inv_freq = nullptr;
+    // per-step scratch (grow-only)
+    int cap_rows = 0, cap_runs = 0, cap_want = 0;
+    uint8_t* h_meta = nullptr;          // pinned
+    uint8_t* d_meta = nullptr;
+    size_t meta_bytes = 0;
+    float *x = nullptr, *P = nullptr, *qbuf = nullptr, *O = nullptr, *conv = nullptr, *logits = nullptr;
+    void *hn = nullptr, *act_a = nullptr, *act_b = nullptr, *hw = nullptr;
+    int* pick = nullptr;
+    float* h_logits = nullptr;          // pinned
+    size_t h_logits_bytes = 0;
+    int max_in = 0, max_act = 0, max_o = 0, max_conv = 0, max_q = 0;
+    float* taps = nullptr;
+    size_t taps_floats = 0;
+    int taps_len = 0;
+    uint64_t launches = 0, weight_bytes = 0, kv_bytes_per_pos = 0;
+};
+
+namespace {
+
+int lp_fail(std::string* err, int code, const std::string& msg) {
+    if (err) *err = msg;
+    return code;
+}
+#define LCU(expr)                                                                                                     \
+    do {                                                                                                              \
+        cudaError_t e_ = (expr);                                                                                      \
+        if (e_ != cudaSuccess) return lp_fail(err, B200_ERR_OPERATION_FAILED, std::string(#expr) + ": " + cudaGetErrorString(e_)); \
+    } while (0)
+#define LCU_ALLOC(expr)                                                                                                \
+    do {                                                                                                               \
+        cudaError_t e_ = (expr);                                                                                       \
+        if (e_ != cudaSuccess) return lp_fail(err, B200_ERR_ALLOCATION_FAILED, std::string(#expr) + ": " + cudaGetErrorString(e_)); \
+    } while (0)
+
+size_t elt(const LpModel* m) { return m->f32 ? 4 : 2; }
+size_t up16(size_t v) { return (v + 255) & ~(size_t)255; }
+
+uint16_t f32_to_bf16(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+    u += 0x7fffu + ((u >> 16) & 1);
+    return (uint16_t)(u >> 16);
+}
+float bf16_to_f32(uint16_t h) {
+    const uint32_t u = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+float f16_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    int exp = (h >> 10) & 0x1f;
+    uint32_t man = h & 0x3ffu;
+    uint32_t u;
+    if (exp == 0) {
+        if (!man) u = sign;
+        else {
+            exp = 127 - 15 + 1;
+            while (!(man & 0x400u)) { man <<= 1; exp--; }
+            u = sign | ((uint32_t)exp << 23) | ((man & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) u = sign | 0x7f800000u | (man << 13);
+    else u = sign | ((uint32_t)(exp - 15 + 127) << 23) | (man << 13);
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+bool is_matrix_name(const std::string& n) {
+    // everything a GEMM or the embedding gather reads; the rest (norm weights, biases, convolution taps, per-head constants, step
+    // vectors) is kept in f32
+    if (n == "embed" || n == "head") return true;
+    static const char* suf[] = {".q", ".k", ".v", ".g", ".o", ".i", ".f", ".a", ".b", ".up", ".down"};
+    for (const char* s : suf) {
+        const size_t L = strlen(s);
+        if (n.size() > L && n.compare(n.size() - L, L, s) == 0) return true;
+    }
+    return false;
+}
+
+const Tensor* find(const LpModel* m, const std::string& name) {
+    auto it = m->tensors.find(name);
+    return it == m->tensors.end() ? nullptr : &it->second;
+}
+
+template <typename... KArgs, typename... Args>
+void launch(LpModel* m, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    kern<<<grid, block, smem, m->stream>>>(std::forward<Args>(args)...);
+    m->launches++;
+}
+
+// Y = epi(alpha X W^T): rows of the step against a [N][K] matrix in the compute type
+template <typename T>
+void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
+    const T* x = (const T*)X;
+    const T* w = (const T*)W;
+    if (R <= 2 * GV_ROWS) {
+        constexpr int VN = Vec8<T>::N;
+        const int vec_ok = (K % VN == 0 && ldx % VN == 0 && ((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0) ? 1 : 0;
+        dim3 grid((N + 7) / 8), block(256);
+        if (epi == EPI_STORE) launch(m, lp_gemv_kernel<T, EPI_STORE>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok);
+        else if (epi == EPI_ADD) launch(m, lp_gemv_kernel<T, EPI_ADD>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok);
+        else launch(m, lp_gemv_kernel<T, EPI_RELU2>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok);
+        return;
+    }
+    dim3 grid((N + GB - 1) / GB, (R + GB - 1) / GB), block(256);
+    if (epi == EPI_STORE) launch(m, lp_gemm_kernel<T, EPI_STORE>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha);
+    else if (epi == EPI_ADD) launch(m, lp_gemm_kernel<T, EPI_ADD>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha);
+    else launch(m, lp_gemm_kernel<T, EPI_RELU2>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha);
+}
+void gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
+    if (m->f32) gemm_t<float>(m, X, ldx, W, N, K, Y, ldy, R, alpha, epi);
+    else gemm_t<bf16>(m, X, ldx, W, N, K, Y, ldy, R, alpha, epi);
+}
+
+void rmsnorm(LpModel* m, float* x, const float* add, const float* w, void* out, const int* gather, int rows) {
+    if (m->f32) launch(m, lp_rmsnorm_kernel<float>, dim3(rows), dim3(128), 0, x, add, w, (float*)out, gather, m->p.width, m->p.norm_eps);
+    else launch(m, lp_rmsnorm_kernel<bf16>, dim3(rows), dim3(128), 0, x, add, w, (bf16*)out, gather, m->p.width, m->p.norm_eps);
+}
+
+int pick_dmax(int dim) { return dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : 256; }
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------ create / upload / finalize
+int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int device, cudaStream_t stream, bool taps, LpModel** out,
+              std::string* err) {
+    if (!prog || !layers || !out) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_ctx_create_layers: null argument");
+    const b200_program_desc& p = *prog;
+    auto bad = [&](const std::string& s) { return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_ctx_create_layers: " + s); };
+    if (p.width <= 0 || p.vocab <= 0 || p.n_layers <= 0 || p.max_seq_len <= 0 || p.max_batch <= 0) return bad("non-positive model dimension");
+    if (p.compute != B200_COMPUTE_BF16 && p.compute != B200_COMPUTE_F32) return bad("compute must be B200_COMPUTE_BF16 or B200_COMPUTE_F32");
+    const bool looped = p.loop_stop > p.loop_start;
+    if (looped && (p.loop_start < 0 || p.loop_stop > p.n_layers || p.loop_times < 1)) return bad("bad repeated layer range");
+    for (int i = 0; i < p.n_layers; i++) {
+        const b200_layer_desc& L = layers[i];
+        const std::string at = "layer " + std::to_string(i) + ": ";
+        if (L.mixer == B200_MIX_WINDOW_MEMORY) {
+            const b200_window_attn_desc& a = L.attn;
+            const b200_matrix_memory_desc& mm = L.mem;
+            if (a.heads <= 0 || a.kv_heads <= 0 || a.dim <= 0 || a.vdim <= 0 || a.heads % a.kv_heads) return bad(at + "bad attention head counts or sizes");
+            if (a.window <= 0 || a.keep_first < 0) return bad(at + "window must be positive, keep_first non-negative");
+            if (a.vdim > 32 * ATT_ACC) return bad(at + "attention value size above " + std::to_string(32 * ATT_ACC));
+            if (mm.heads <= 0 || mm.dim <= 0 || mm.vdim <= 0 || !(mm.gate_cap > 0.0f)) return bad(at + "bad matrix-memory sizes");
+            if (mm.dim > 256) return bad(at + "matrix-memory key size above 256");
+        } else if (L.mixer == B200_MIX_GATED_DELTA) {
+            const b200_gated_delta_desc& g = L.delta;
+            if (g.heads <= 0 || g.kv_heads <= 0 || g.dim <= 0 || g.vdim <= 0 || g.heads % g.kv_heads || g.conv < 1) return bad(at + "bad delta-rule sizes");
+            if (g.dim > 256) return bad(at + "delta-rule key size above 256");
+        } else return bad(at + "unknown mixer");
+        if (L.ff < 0) return bad(at + "negative feed-forward width");
+    }
+    LpModel* m = new LpModel();
+    m->p = p;
+    m->layers.assign(layers, layers + p.n_layers);
+    m->device = device;
+    m->stream = stream;
+    m->f32 = p.compute == B200_COMPUTE_F32;
+    m->taps_on = taps;
+    // the order of layer runs: [0, start) once, [start, stop) `times` times, [stop, n) once
+    auto push = [&](int li, int pass) {
+        m->runs.push_back(li);
+        m->run_pass.push_back(pass);
+    };
+    if (looped) {
+        for (int i = 0; i < p.loop_start; i++) push(i, -1);
+        for (int t = 0; t < p.loop_times; t++)
+            for (int i = p.loop_start; i < p.loop_stop; i++) push(i, i == p.loop_start ? t : -1);
+        for (int i = p.loop_stop; i < p.n_layers; i++) push(i, -1);
+    } else {
+        for (int i = 0; i < p.n_layers; i++) push(i, -1);
+    }
+    m->slot.resize(p.max_batch);
+    *out = m;
+    return B200_OK;
+}
+
+int lp_upload(LpModel* m, const char* name, uint32_t type, const uint64_t* ne, int n_dims, const void* host, size_t nbytes, std::string* err) {
+    if (m->finalized) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_ctx_upload_tensor: context already finalized");
+    if (n_dims < 1 || n_dims > 2) return lp_fail(err, B200_ERR_SHAPE_MISMATCH, std::string(name) + ": 1 or 2 dims expected");
+    size_t es;
+    if (type == B200_TYPE_BF16 || type == B200_TYPE_F16) es = 2;
+    else if (type == B200_TYPE_F32) es = 4;
+    else return lp_fail(err, B200_ERR_UNSUPPORTED_DTYPE, std::string(name) + ": layer-program contexts take BF16, F16 or F32 tensors");
+    const uint64_t cols = ne[0], rows = n_dims == 2 ? ne[1] : 1;
+    const uint64_t numel = cols * rows;
+    if (numel * es != nbytes) return lp_fail(err, B200_ERR_SHAPE_MISMATCH, std::string(name) + ": byte size does not match shape");
+    const std::string nm(name);
+    Tensor t;
+    t.matrix = is_matrix_name(nm) && n_dims == 2;
+    t.rows = rows;
+    t.cols = cols;
+    const bool store_bf16 = t.matrix && !m->f32;
+    std::vector<uint8_t> conv;
+    const void* src = host;
+    if (store_bf16) {
+        if (type != B200_TYPE_BF16) {
+            conv.resize(numel * 2);
+            uint16_t* o = (uint16_t*)conv.data();
+            for (uint64_t i = 0; i < numel; i++)
+                o[i] = f32_to_bf16(type == B200_TYPE_F32 ? ((const float*)host)[i] : f16_to_f32(((const uint16_t*)host)[i]));
+            src = conv.data();
+        }
+        t.bytes = numel * 2;
+    } else {
+        if (type != B200_TYPE_F32) {
+            conv.resize(numel * 4);
+            float* o = (float*)conv.data();
+            for (uint64_t i = 0; i < numel; i++)
+                o[i] = type == B200_TYPE_BF16 ? bf16_to_f32(((const uint16_t*)host)[i]) : f16_to_f32(((const uint16_t*)host)[i]);
+            src = conv.data();
+        }
+        t.bytes = numel * 4;
+    }
+    LCU(cudaSetDevice(m->device));
+    auto old = m->tensors.find(nm);
+    if (old != m->tensors.end()) cudaFree(old->second.d);
+    LCU_ALLOC(cudaMalloc(&t.d, up16(t.bytes)));
+    LCU(cudaMemcpy(t.d, src, t.bytes, cudaMemcpyHostToDevice));
+    m->tensors[nm] = t;
+    return B200_OK;
+}
+
+namespace {
+// Concatenate the rows of several [n_i][K] matrices into one device matrix; the pieces are freed.
+int fuse_rows(LpModel* m, const std::vector<std::string>& names, const std::vector<uint64_t>& want_rows, uint64_t K, void** out, int* n_out,
+              std::vector<int>* offs, std::string* err) {
+    uint64_t total = 0;
+    for (size_t i = 0; i < names.size(); i++) {
+        const Tensor* t = find(m, names[i]);
+        if (!t) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "missing tensor " + names[i]);
+        if (!t->matrix || t->cols != K || t->rows != want_rows[i])
+            return lp_fail(err, B200_ERR_SHAPE_MISMATCH, names[i] + ": expected [" + std::to_string(want_rows[i]) + ", " + std::to_string(K) + "], got [" +
+                                                             std::to_string(t->rows) + ", " + std::to_string(t->cols) + "]");
+        offs->push_back((int)total);
+        total += t->rows;
+    }
+    void* d = nullptr;
+    LCU_ALLOC(cudaMalloc(&d, up16(total * K * elt(m))));
+    size_t off = 0;
+    for (const std::string& n : names) {
+        Tensor& t = m->tensors[n];
+        LCU(cudaMemcpy((uint8_t*)d + off, t.d, t.bytes, cudaMemcpyDeviceToDevice));
+        off += t.bytes;
+        cudaFree(t.d);
+        m->weight_bytes += t.bytes;
+        m->tensors.erase(n);
+    }
+    *out = d;
+    *n_out = (int)total;
+    return B200_OK;
+}
+int need_vec(LpModel* m, const std::string& name, uint64_t n, const float** out, std::string* err) {
+    const Tensor* t = find(m, name);
+    if (!t) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "missing tensor " + name);
+    if (t->matrix || t->rows * t->cols != n)
+        return lp_fail(err, B200_ERR_SHAPE_MISMATCH, name + ": expected " + std::to_string(n) + " values, got " + std::to_string(t->rows * t->cols));
+    *out = (const float*)t->d;
+    m->weight_bytes += t->bytes;
+    return B200_OK;
+}
+int need_mat(LpModel* m, const std::string& name, uint64_t rows, uint64_t cols, void** out, std::string* err) {
+    const Tensor* t = find(m, name);
+    if (!t) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "missing tensor " + name);
+    if (!t->matrix || t->rows != rows || t->cols != cols)
+        return lp_fail(err, B200_ERR_SHAPE_MISMATCH, name + ": expected [" + std::to_string(rows) + ", " + std::to_string(cols) + "], got [" +
+                                                         std::to_string(t->rows) + ", " + std::to_string(t->cols) + "]");
+    *out = t->d;
+    m->weight_bytes += t->bytes;
+    return B200_OK;
+}
+}  // namespace
+
+int lp_finalize(LpModel* m, std::string* err) {
+    if (m->finalized) return B200_OK;
+    LCU(cudaSetDevice(m->device));
+    const b200_program_desc& p = m->p;
+    const uint64_t W = p.width;
+    int rc;
+    m->plan.resize(p.n_layers);
+    void* dummy;
+    if ((rc = need_mat(m, "embed", p.vocab, W, &dummy, err))) return rc;
+    m->weight_bytes -= find(m, "embed")->bytes - W * elt(m);   // one row per token
+    if ((rc = need_mat(m, "head", p.vocab, W, &dummy, err))) return rc;
+    const float* fv;
+    if ((rc = need_vec(m, "final.norm", W, &fv, err))) return rc;
+    if (p.loop_stop > p.loop_start && (rc = need_vec(m, "loop.step", (uint64_t)p.loop_times * W, &fv, err))) return rc;
+    for (int li = 0; li < p.n_layers; li++) {
+        LayerPlan& L = m->plan[li];
+        L.d = m->layers[li];
+        const std::string pre = "l" + std::to_string(li) + ".";
+        if ((rc = need_vec(m, pre + "norm1", W, &L.norm1, err))) return rc;
+        std::vector<int> off;
+        if (L.d.mixer == B200_MIX_WINDOW_MEMORY) {
+            const b200_window_attn_desc& a = L.d.attn;
+            const b200_matrix_memory_desc& mm = L.d.mem;
+            const std::string l = pre + "mix.left.", r = pre + "mix.right.";
+            std::vector<std::string> names = {l + "q", l + "k", l + "v"};
+            std::vector<uint64_t> rows = {(uint64_t)a.heads * a.dim, (uint64_t)a.kv_heads * a.dim, (uint64_t)a.kv_heads * a.vdim};
+            if (a.out_gate) { names.push_back(l + "g"); rows.push_back((uint64_t)a.heads * a.vdim); }
+            const size_t n_left = names.size();
+            for (const char* s : {"q", "k", "v", "g", "i", "f"}) names.push_back(r + s);
+            for (uint64_t v : {(uint64_t)mm.heads * mm.dim, (uint64_t)mm.heads * mm.dim, (uint64_t)mm.heads * mm.vdim, (uint64_t)mm.heads * mm.vdim,
+                               (uint64_t)mm.heads, (uint64_t)mm.heads})
+                rows.push_back(v);
+            if ((rc = fuse_rows(m, names, rows, W, &L.w_in, &L.n_in, &off, err))) return rc;
+            AttnGeom& g = L.ag;
+            g.H = a.heads; g.G = a.kv_heads; g.dim = a.dim; g.vdim = a.vdim; g.window = a.window; g.keep_first = a.keep_first;
+            g.qk_norm = a.qk_norm; g.out_gate = a.out_gate; g.scale = a.scale; g.eps = p.norm_eps; g.cap = p.max_seq_len;
+            g.q_off = off[0]; g.k_off = off[1]; g.v_off = off[2]; g.g_off = a.out_gate ? off[3] : 0;
+            MemGeom& q = L.mg;
+            q.H = mm.heads; q.dim = mm.dim; q.vdim = mm.vdim; q.cap = mm.gate_cap;
+            q.q_off = off[n_left]; q.k_off = off[n_left + 1]; q.v_off = off[n_left + 2]; q.i_off = off[n_left + 4]; q.f_off = off[n_left + 5];
+            L.dg.g_off = off[n_left + 3];   // (gate columns of the memory branch)
+            if (a.qk_norm) {
+                if ((rc = need_vec(m, l + "q.norm", a.dim, &L.qn, err))) return rc;
+                if ((rc = need_vec(m, l + "k.norm", a.dim, &L.kn, err))) return rc;
+            }
+            if ((rc = need_mat(m, l + "o", W, (uint64_t)a.heads * a.vdim, &L.wo_attn, err))) return rc;
+            if ((rc = need_mat(m, r + "o", W, (uint64_t)mm.heads * mm.vdim, &L.wo_mem, err))) return rc;
+            if ((rc = need_vec(m, r + "norm", (uint64_t)mm.heads * mm.vdim, &L.mem_norm, err))) return rc;
+            if ((rc = need_vec(m, r + "i.b", mm.heads, &L.ib, err))) return rc;
+            if ((rc = need_vec(m, r + "f.b", mm.heads, &L.fb, err))) return rc;
+            L.kv_bytes = up16((size_t)p.max_seq_len * a.kv_heads * (a.dim + a.vdim) * 4);
+            L.rec_bytes = up16(((size_t)mm.heads * mm.dim * mm.vdim + (size_t)mm.heads * mm.dim + mm.heads) * 4);
+            m->max_act = std::max(m->max_act, std::max(a.heads * a.vdim, mm.heads * mm.vdim));
+            m->max_o = std::max(m->max_o, mm.heads * mm.vdim);
+            m->max_q = std::max(m->max_q, a.heads * a.dim);
+        } else {
+            const b200_gated_delta_desc& g = L.d.delta;
+            const std::string x = pre + "mix.";
+            const uint64_t qk = (uint64_t)g.kv_heads * g.dim, vv = (uint64_t)g.heads * g.vdim;
+            std::vector<std::string> names = {x + "q", x + "k", x + "v", x + "g", x + "b", x + "a"};
+            std::vector<uint64_t> rows = {qk, qk, vv, vv, (uint64_t)g.heads, (uint64_t)g.heads};
+            if ((rc = fuse_rows(m, names, rows, W, &L.w_in, &L.n_in, &off, err))) return rc;
+            DeltaGeom& d = L.dg;
+            d.H = g.heads; d.G = g.kv_heads; d.dim = g.dim; d.vdim = g.vdim; d.taps = g.conv; d.C = (int)(2 * qk + vv);
+            d.g_off = off[3]; d.b_off = off[4]; d.a_off = off[5]; d.eps = p.norm_eps;
+            // the three convolutions as one [C][taps] table in the column order of the projection
+            const float *cq, *ck, *cv;
+            if ((rc = need_vec(m, x + "q.conv", qk * g.conv, &cq, err))) return rc;
+            if ((rc = need_vec(m, x + "k.conv", qk * g.conv, &ck, err))) return rc;
+            if ((rc = need_vec(m, x + "v.conv", vv * g.conv, &cv, err))) return rc;
+            float* cw = nullptr;
+            LCU_ALLOC(cudaMalloc((void**)&cw, up16((size_t)d.C * g.conv * 4)));
+            LCU(cudaMemcpy(cw, cq, qk * g.conv * 4, cudaMemcpyDeviceToDevice));
+            LCU(cudaMemcpy(cw + qk * g.conv, ck, qk * g.conv * 4, cudaMemcpyDeviceToDevice));
+            LCU(cudaMemcpy(cw + 2 * qk * g.conv, cv, vv * g.conv * 4, cudaMemcpyDeviceToDevice));
+            Tensor t;
+            t.d = cw; t.rows = d.C; t.cols = g.conv; t.bytes = (size_t)d.C * g.conv * 4;
+            m->tensors[x + "qkv.conv"] = t;
+            L.conv_w = cw;
+            if ((rc = need_vec(m, x + "A_log", g.heads, &L.A_log, err))) return rc;
+            if ((rc = need_vec(m, x + "dt_bias", g.heads, &L.dt_bias, err))) return rc;
+            if ((rc = need_vec(m, x + "norm", g.vdim, &L.delta_norm, err))) return rc;
+            if ((rc = need_mat(m, x + "o", W, vv, &L.wo_delta, err))) return rc;
+            L.rec_bytes = up16(((size_t)g.heads * g.dim * g.vdim + (size_t)std::max(0, g.conv - 1) * d.C) * 4);
+            m->max_act = std::max(m->max_act, (int)vv);
+            m->max_o = std::max(m->max_o, (int)vv);
+            m->max_conv = std::max(m->max_conv, d.C);
+        }
+        m->max_in = std::max(m->max_in, L.n_in);
+        if (L.d.ff > 0) {
+            if ((rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
+            if ((rc = need_mat(m, pre + "mlp.up", L.d.ff, W, &L.w_up, err))) return rc;
+            if ((rc = need_mat(m, pre + "mlp.down", W, L.d.ff, &L.w_down, err))) return rc;
+            m->max_act = std::max(m->max_act, L.d.ff);
+        }
+    }
+    // layout of a slot: cache block (all runs with attention) and state block (all runs)
+    size_t kv = 0, rec = 0;
+    for (size_t r = 0; r < m->runs.size(); r++) {
+        const LayerPlan& L = m->plan[m->runs[r]];
+        m->run_kv_off.push_back(kv);
+        m->run_rec_off.push_back(rec);
+        kv += L.kv_bytes;
+        rec += L.rec_bytes;
+        m->weight_bytes += 0;
+        if (L.d.mixer == B200_MIX_WINDOW_MEMORY) m->kv_bytes_per_pos += (size_t)L.d.attn.kv_heads * (L.d.attn.dim + L.d.attn.vdim) * 4;
+    }
+    m->slot_kv_bytes = std::max<size_t>(kv, 256);
+    m->slot_rec_bytes = std::max<size_t>(rec, 256);
+    // frequencies of the sinusoidal position vector, in double
+    {
+        const int nf = (p.width + 1) / 2;
+        std::vector<double> f(nf);
+        for (int i = 0; i < nf; i++) f[i] = std::pow(10000.0, -2.0 * (double)i / (double)p.width);
+        LCU_ALLOC(cudaMalloc((void**)&m->inv_freq, up16(nf * sizeof(double))));
+        LCU(cudaMemcpy(m->inv_freq, f.data(), nf * sizeof(double), cudaMemcpyHostToDevice));
+    }
+    m->finalized = true;
+    return B200_OK;
+}
+
+void lp_destroy(LpModel* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    cudaStreamSynchronize(m->stream);
+    for (auto& kv : m->tensors) cudaFree(kv.second.d);
+    for (LayerPlan& L : m->plan) cudaFree(L.w_in);
+    for (SlotMem& s : m->slot) { cudaFree(s.kv); cudaFree(s.rec); }
+    for (SlotMem& s : m->pool) { cudaFree(s.kv); cudaFree(s.rec); }
+    for (void* ptr : {(void*)m->inv_freq, (void*)m->d_meta, (void*)m->x, (void*)m->P, (void*)m->qbuf, (void*)m->O, (void*)m->conv, (void*)m->logits,
+                      m->hn, m->act_a, m->act_b, m->hw, (void*)m->pick, (void*)m->taps})
+        cudaFree(ptr);
+    if (m->h_meta) cudaFreeHost(m->h_meta);
+    if (m->h_logits) cudaFreeHost(m->h_logits);
+    delete m;
+}
+
+int lp_layer_runs(const LpModel* m) { return (int)m->runs.size(); }
+
+void lp_stats(const LpModel* m, uint64_t* launches, uint64_t* weight_bytes, uint64_t* kv_bytes_per_pos) {
+    if (launches) *launches = m->launches;
+    if (weight_bytes) *weight_bytes = m->weight_bytes;
+    if (kv_bytes_per_pos) *kv_bytes_per_pos = m->kv_bytes_per_pos;
+}
+
+void lp_pool_counts(const LpModel* m, int* live, int* pooled) {
+    int n = 0;
+    for (const SlotMem& s : m->slot) n += s.rec != nullptr;
+    if (live) *live = n;
+    if (pooled) *pooled = (int)m->pool.size();
+}
+
+int lp_release(LpModel* m, int seq, std::string* err) {
+    if (seq < 0 || seq >= (int)m->slot.size()) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "bad sequence slot");
+    if (m->slot[seq].rec) {
+        m->pool.push_back(m->slot[seq]);
+        m->slot[seq] = SlotMem();
+    }
+    return B200_OK;
+}
+
+int lp_get_taps(LpModel* m, float* out, size_t cap_floats, std::string* err) {
+    if (!m->taps_on) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_get_taps: taps are off (B200_TAPS=1 before the context is created)");
+    const size_t n = (size_t)m->runs.size() * m->taps_len * m->p.width;
+    if (!out || cap_floats < n) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_get_taps: buffer too small");
+    LCU(cudaSetDevice(m->device));
+    LCU(cudaMemcpy(out, m->taps, n * 4, cudaMemcpyDeviceToHost));
+    return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ the step
+namespace {
+template <typename P>
+int grow(P** ptr, size_t bytes, std::string* err) {
+    cudaFree(*ptr);
+    *ptr = nullptr;
+    LCU_ALLOC(cudaMalloc((void**)ptr, up16(bytes)));
+    return B200_OK;
+}
+
+int ensure_scratch(LpModel* m, int R, int n_runs, int n_want, std::string* err) {
+    int rc;
+    const size_t es = elt(m);
+    const int W = m->p.width;
+    if (R > m->cap_rows) {
+        const int cap = std::max(R, std::min(2 * m->cap_rows, 1 << 20));
+        if ((rc = grow(&m->x, (size_t)cap * W * 4, err))) return rc;
+        if ((rc = grow(&m->P, (size_t)cap * m->max_in * 4, err))) return rc;
+        if ((rc = grow(&m->qbuf, (size_t)cap * std::max(m->max_q, 1) * 4, err))) return rc;
+        if ((rc = grow(&m->O, (size_t)cap * m->max_o * 4, err))) return rc;
+        if ((rc = grow(&m->conv, (size_t)cap * std::max(m->max_conv, 1) * 4, err))) return rc;
+        if ((rc = grow(&m->hn, (size_t)cap * W * es, err))) return rc;
+        if ((rc = grow(&m->act_a, (size_t)cap * m->max_act * es, err))) return rc;
+        if ((rc = grow(&m->act_b, (size_t)cap * m->max_act * es, err))) return rc;
+        m->cap_rows = cap;
+    }
+    if (n_want > m->cap_want) {
+        const int cap = std::max(n_want, 2 * m->cap_want);
+        if ((rc = grow(&m->logits, (size_t)cap * m->p.vocab * 4, err))) return rc;
+        if ((rc = grow(&m->hw, (size_t)cap * W * es, err))) return rc;
+        if ((rc = grow(&m->pick, (size_t)cap * 4, err))) return rc;
+        m->cap_want = cap;
+    }
+    m->cap_runs = std::max(m->cap_runs, n_runs);
+    const size_t meta = up16((size_t)(3 * m->cap_rows + 2 * m->cap_runs + 2 + m->cap_want) * 4) + (size_t)2 * m->cap_runs * 8 + 64;
+    if (meta > m->meta_bytes) {
+        if (m->h_meta) cudaFreeHost(m->h_meta);
+        m->h_meta = nullptr;
+        LCU_ALLOC(cudaHostAlloc((void**)&m->h_meta, meta, cudaHostAllocDefault));
+        if ((rc = grow(&m->d_meta, meta, err))) return rc;
+        m->meta_bytes = meta;
+    }
+    return B200_OK;
+}
+}  // namespace
+
+int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int* lens, const uint32_t* tokens, const int* want_rows, int n_want,
+            float* logits_out, uint32_t* pick_out, std::string* err) {
+    if (!m->finalized) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: context not finalized");
+    if (n_runs <= 0 || !seqs || !lens || !tokens || !pos0) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: bad argument");
+    if (n_want < 0 || (n_want > 0 && !want_rows)) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: bad want_rows");
+    const b200_program_desc& p = m->p;
+    int R = 0;
+    for (int i = 0; i < n_runs; i++) {
+        if (seqs[i] < 0 || seqs[i] >= (int)m->slot.size()) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: bad sequence slot");
+        for (int j = 0; j < i; j++)
+            if (seqs[i] == seqs[j]) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: duplicate sequence slot");
+        if (lens[i] <= 0) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: empty token run");
+        if ((int64_t)pos0[i] + lens[i] > p.max_seq_len) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: context length exceeded");
+        R += lens[i];
+    }
+    for (int r = 0; r < R; r++)
+        if (tokens[r] >= (uint32_t)p.vocab) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: token id " + std::to_string(tokens[r]) + " exceeds vocab size");
+    for (int i = 0; i < n_want; i++)
+        if (want_rows[i] < 0 || want_rows[i] >= R) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: want_rows out of range");
+    LCU(cudaSetDevice(m->device));
+    int rc;
+    if ((rc = ensure_scratch(m, R, n_runs, n_want, err))) return rc;
+    // slot memory: a slot at position 0 starts from a zeroed state block (out of the pool when one is waiting there)
+    for (int i = 0; i < n_runs; i++) {
+        SlotMem& s = m->slot[seqs[i]];
+        if (pos0[i] == 0 && s.rec) {   // (a slot that was rewound without a release)
+            m->pool.push_back(s);
+            s = SlotMem();
+        }
+        if (!s.rec) {
+            if (pos0[i] != 0) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "b200_step: the slot holds no state for its position");
+            if (!m->pool.empty()) {
+                s = m->pool.back();
+                m->pool.pop_back();
+            } else {
+                LCU_ALLOC(cudaMalloc((void**)&s.kv, m->slot_kv_bytes));
+                cudaError_t e = cudaMalloc((void**)&s.rec, m->slot_rec_bytes);
+                if (e != cudaSuccess) {
+                    cudaFree(s.kv);
+                    s = SlotMem();
+                    return lp_fail(err, B200_ERR_ALLOCATION_FAILED, std::string("slot state: ") + cudaGetErrorString(e));
+                }
+            }
+            LCU(cudaMemsetAsync(s.rec, 0, m->slot_rec_bytes, m->stream));
+        }
+    }
+    // tables of the step
+    StepMeta sm{};
+    {
+        int* hi = (int*)m->h_meta;
+        int* tok = hi;
+        int* row_run = tok + m->cap_rows;
+        int* row_pos = row_run + m->cap_rows;
+        int* run_start = row_pos + m->cap_rows;
+        int* run_p0 = run_start + m->cap_runs + 1;
+        int* want = run_p0 + m->cap_runs + 1;
+        const size_t ints = up16((size_t)(3 * m->cap_rows + 2 * m->cap_runs + 2 + m->cap_want) * 4);
+        uint8_t** kvp = (uint8_t**)(m->h_meta + ints);
+        uint8_t** recp = kvp + m->cap_runs;
+        int r = 0;
+        for (int i = 0; i < n_runs; i++) {
+            run_start[i] = r;
+            run_p0[i] = pos0[i];
+            kvp[i] = m->slot[seqs[i]].kv;
+            recp[i] = m->slot[seqs[i]].rec;
+            for (int t = 0; t < lens[i]; t++, r++) {
+                tok[r] = (int)tokens[r];
+                row_run[r] = i;
+                row_pos[r] = pos0[i] + t;
+            }
+        }
+        run_start[n_runs] = r;
+        for (int i = 0; i < n_want; i++) want[i] = want_rows[i];
+        LCU(cudaMemcpyAsync(m->d_meta, m->h_meta, m->meta_bytes, cudaMemcpyHostToDevice, m->stream));
+        const uint8_t* d = m->d_meta;
+        sm.tok = (const int*)d;
+        sm.row_run = sm.tok + m->cap_rows;
+        sm.row_pos = sm.row_run + m->cap_rows;
+        sm.run_start = sm.row_pos + m->cap_rows;
+        sm.run_pos0 = sm.run_start + m->cap_runs + 1;
+        sm.want = sm.run_pos0 + m->cap_runs + 1;
+        sm.run_kv = (uint8_t* const*)(d + ints);
+        sm.run_rec = sm.run_kv + m->cap_runs;
+    }
+    const int W = p.width;
+    const float* loop_step = p.loop_stop > p.loop_start ? (const float*)find(m, "loop.step")->d : nullptr;
+    if (m->taps_on) {
+        const size_t need = (size_t)m->runs.size() * lens[0] * W;
+        if (need > m->taps_floats) {
+            if ((rc = grow(&m->taps, need * 4, err))) return rc;
+            m->taps_floats = need;
+        }
+        m->taps_len = lens[0];
+    }
+    // embedding
+    if (m->f32) launch(m, lp_embed_kernel<float>, dim3(R), dim3(128), 0, sm, (const float*)find(m, "embed")->d, m->inv_freq, m->x, W, p.embed_scale, p.pos_sinusoid);
+    else launch(m, lp_embed_kernel<bf16>, dim3(R), dim3(128), 0, sm, (const bf16*)find(m, "embed")->d, m->inv_freq, m->x, W, p.embed_scale, p.pos_sinusoid);
+    for (size_t run = 0; run < m->runs.size(); run++) {
+        LayerPlan& L = m->plan[m->runs[run]];
+        const float* add = m->run_pass[run] >= 0 ? loop_step + (size_t)m->run_pass[run] * W : nullptr;
+        rmsnorm(m, m->x, add, L.norm1, m->hn, nullptr, R);
+        gemm(m, m->hn, W, L.w_in, L.n_in, W, m->P, L.n_in, R, 1.0f, EPI_STORE);
+        if (L.d.mixer == B200_MIX_WINDOW_MEMORY) {
+            AttnGeom ag = L.ag;
+            ag.kv_off = m->run_kv_off[run];
+            launch(m, lp_attn_prep_kernel, dim3(R), dim3(128), 0, sm, ag, (const float*)m->P, L.n_in, L.qn, L.kn, m->qbuf);
+            const int wpb = 4;
+            dim3 agrid(R, (ag.H + wpb - 1) / wpb);
+            const size_t asmem = (size_t)wpb * ag.dim * 4;
+            if (m->f32) launch(m, lp_window_attn_kernel<float>, agrid, dim3(32 * wpb), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (float*)m->act_a);
+            else launch(m, lp_window_attn_kernel<bf16>, agrid, dim3(32 * wpb), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (bf16*)m->act_a);
+            MemGeom mg = L.mg;
+            mg.rec_off = m->run_rec_off[run];
+            const int ldo = mg.H * mg.vdim;
+            dim3 sgrid((mg.vdim + SCAN_BD - 1) / SCAN_BD, mg.H, n_runs);
+            switch (pick_dmax(mg.dim)) {
+                case 32: launch(m, lp_matrix_memory_kernel<32>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
+                case 64: launch(m, lp_matrix_memory_kernel<64>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
+                case 128: launch(m, lp_matrix_memory_kernel<128>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
+                default: launch(m, lp_matrix_memory_kernel<256>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
+            }
+            dim3 hgrid(R, (mg.H + 3) / 4);
+            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (float*)m->act_b, R);
+            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (bf16*)m->act_b, R);
+            gemm(m, m->act_a, ag.H * ag.vdim, L.wo_attn, W, ag.H * ag.vdim, m->x, W, R, L.d.attn_scale, EPI_ADD);
+            gemm(m, m->act_b, ldo, L.wo_mem, W, ldo, m->x, W, R, L.d.mem_scale, EPI_ADD);
+        } else {
+            DeltaGeom dg = L.dg;
+            dg.rec_off = m->run_rec_off[run];
+            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, m->conv);
+            if (dg.taps > 1) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
+            const int ldo = dg.H * dg.vdim;
+            dim3 sgrid((dg.vdim + SCAN_BD - 1) / SCAN_BD, dg.H, n_runs);
+            switch (pick_dmax(dg.dim)) {
+                case 32: launch(m, lp_gated_delta_kernel<32>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
+                case 64: launch(m, lp_gated_delta_kernel<64>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
+                case 128: launch(m, lp_gated_delta_kernel<128>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
+                default: launch(m, lp_gated_delta_kernel<256>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
+            }
+            dim3 hgrid(R, (dg.H + 3) / 4);
+            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (float*)m->act_a, R);
+            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (bf16*)m->act_a, R);
+            gemm(m, m->act_a, ldo, L.wo_delta, W, ldo, m->x, W, R, 1.0f, EPI_ADD);
+        }
+        if (L.d.ff > 0) {
+            rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
+            gemm(m, m->hn, W, L.w_up, L.d.ff, W, m->act_a, L.d.ff, R, 1.0f, EPI_RELU2);
+            gemm(m, m->act_a, L.d.ff, L.w_down, W, L.d.ff, m->x, W, R, 1.0f, EPI_ADD);
+        }
+        if (m->taps_on) LCU(cudaMemcpyAsync(m->taps + run * (size_t)lens[0] * W, m->x, (size_t)lens[0] * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+    }
+    if (n_want > 0 && (logits_out || pick_out)) {
+        rmsnorm(m, m->x, nullptr, (const float*)find(m, "final.norm")->d, m->hw, sm.want, n_want);
+        gemm(m, m->hw, W, find(m, "head")->d, p.vocab, W, m->logits, p.vocab, n_want, p.logit_scale, EPI_STORE);
+        if (pick_out) {
+            launch(m, lp_argmax_kernel, dim3(n_want), dim3(1024), 0, (const float*)m->logits, p.vocab, m->pick);
+            LCU(cudaMemcpyAsync(pick_out, m->pick, (size_t)n_want * 4, cudaMemcpyDeviceToHost, m->stream));
+        } else {
+            const size_t bytes = (size_t)n_want * p.vocab * 4;
+            if (bytes > m->h_logits_bytes) {
+                if (m->h_logits) cudaFreeHost(m->h_logits);
+                m->h_logits = nullptr;
+                m->h_logits_bytes = 0;
+                LCU_ALLOC(cudaHostAlloc((void**)&m->h_logits, bytes, cudaHostAllocDefault));
+                m->h_logits_bytes = bytes;
+            }
+            LCU(cudaMemcpyAsync(m->h_logits, m->logits, bytes, cudaMemcpyDeviceToHost, m->stream));
+        }
+    }
+    LCU(cudaStreamSynchronize(m->stream));
+    LCU(cudaGetLastError());
+    if (n_want > 0 && logits_out) memcpy(logits_out, m->h_logits, (size_t)n_want * p.vocab * 4);
+    return B200_OK;
+}
