@@ -1,0 +1,167 @@
+"""bench.py --design lazilorn: prefill and decode throughput of the Lazilorn layer program at sizes that resemble a real model's
+layers (random weights), beside the library's closest existing model -- a llama-architecture transformer of the same width, depth
+and parameter count in Q8_0 blocks (the densest weight type its tensor-core prompt path takes).
+
+Per size and model: prompt tokens/s for one prompt of --prefill-len tokens, decode tokens/s at batch 1 and at --batch sequences
+after prompts of --prompt-len tokens.  Every number is host wall clock around the library call (each call ends with a stream
+synchronisation), after warm-up calls, so launch overhead and the copies of tokens and results are inside.  One JSON line."""
+import json
+import sys
+import time
+
+import numpy as np
+
+SIZES = {
+    # name: width, layers (p = attention beside a matrix memory, d = gated delta rule), attention heads / kv heads, ff
+    "w1024": dict(width=1024, pattern="pdppdp", heads=8, kv_heads=2, ff=4096, vocab=32000),
+    "w2048": dict(width=2048, pattern="pdppdppd", heads=16, kv_heads=4, ff=8192, vocab=32000),
+}
+
+
+def lazilorn_config(s, window=1024, keep_first=4):
+    layers = []
+    for ch in s["pattern"]:
+        if ch == "p":
+            layers.append({"type": "parallel", "mlp": {"kind": "dense", "ff": s["ff"]},
+                           "mixer": {"left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128,
+                                              "mask": {"size": window, "keep_first": keep_first}, "scale": 128 ** -0.5},
+                                     "right": {"heads": s["heads"] // 2, "dim": 64, "vdim": 128, "gate_cap": 15.0},
+                                     "left_scale": 0.7, "right_scale": 0.7}})
+        else:
+            layers.append({"type": "delta", "mlp": {"kind": "dense", "ff": s["ff"]},
+                           "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "conv": 4}})
+    return {"architecture": "Lazilorn", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "loop": {"start": 0, "stop": 0, "times": 1}, "layers": layers}
+
+
+def lazilorn_feeder(cfg, seed):
+    """upload(name, type, ne, data) for every tensor of cfg: bf16 bit patterns of N(0, 1/fan_in) matrices, f32 vectors."""
+    import llama_gguf_b200 as B
+    from llama_gguf_b200.safetensors_io import bf16_bits
+    from llama_gguf_b200.lazilorn import tensor_shapes
+
+    def feed(upload):
+        rng = np.random.default_rng(seed)
+        for name, shape in tensor_shapes(cfg).items():
+            last = name.split(".")[-1]
+            if len(shape) == 2 and last != "conv" and name != "loop.step":
+                a = rng.standard_normal(shape, dtype=np.float32) * np.float32(1.0 / np.sqrt(shape[-1]))
+                upload(name, B.BF16, list(reversed(shape)), bf16_bits(a).reshape(shape))
+                continue
+            if last == "conv":
+                a = 0.5 * rng.standard_normal(shape)
+            elif name.endswith("f.b"):
+                a = rng.uniform(1.0, 4.0, shape)
+            elif last in ("A_log", "dt_bias", "b") and len(shape) == 1:
+                a = rng.uniform(-2.0, 0.5, shape)
+            else:
+                a = 1.0 + 0.1 * rng.standard_normal(shape)
+            upload(name, B.F32, list(reversed(shape)), np.ascontiguousarray(a, dtype=np.float32))
+    return feed
+
+
+def n_params(cfg):
+    from llama_gguf_b200.lazilorn import tensor_shapes
+    return int(sum(np.prod(s) for n, s in tensor_shapes(cfg).items() if n != "embed"))
+
+
+def timed(fn, warm, reps):
+    for _ in range(warm):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        fn()
+    return (time.perf_counter() - t0) / reps
+
+
+def bench_lazilorn(cfg, args, max_seq):
+    import llama_gguf_b200 as B
+    from llama_gguf_b200 import lazilorn
+    program, layers = lazilorn.parse_config(cfg, max_seq, max(args.batch, 1) + 1, "bfloat16")
+    gpu = B.LayerProgramInference(program, layers, feeder=lazilorn_feeder(cfg, args.seed))
+    V = cfg["vocab"]
+    rng = np.random.default_rng(args.seed + 1)
+    out = {}
+    if args.prefill_len:
+        toks = [int(t) for t in rng.integers(0, V, args.prefill_len)]
+
+        def one():
+            gpu.reset(0)
+            gpu.step([(0, toks)], [len(toks) - 1])
+        out["prefill_tok_s"] = args.prefill_len / timed(one, 2, 4)
+    st0 = gpu.stats()["kernel_launches"]
+    for nb, key in ((1, "decode_b1_tok_s"), (args.batch, "decode_b%d_tok_s" % args.batch)):
+        if nb < 1:
+            continue
+        for s in range(nb):
+            gpu.reset(s)
+        gpu.step([(s, [int(t) for t in rng.integers(0, V, args.prompt_len)]) for s in range(nb)])
+        state = {"t": [1] * nb}
+
+        def one():
+            state["t"] = gpu.decode_batch_greedy(list(range(nb)), state["t"])
+        out[key] = nb / timed(one, args.warmup, args.steps)
+    out["kernel_launches"] = gpu.stats()["kernel_launches"] - st0
+    out["weight_bytes_per_token"] = gpu.stats()["weight_bytes_per_token"]
+    gpu.close()
+    return out
+
+
+def bench_llama(s, n_layers, ffn, args, max_seq):
+    import llama_gguf_b200 as B
+    from llama_gguf_b200.presets import make_desc
+    from llama_gguf_b200.randmodel import random_model
+    preset = dict(arch="llama", hidden=s["width"], n_layers=n_layers, n_heads=s["width"] // 128, n_kv_heads=s["kv_heads"], head_dim=128,
+                  ffn=ffn, vocab=s["vocab"], norm_eps=1e-5, rope_base=1e4, rope_neox=0, bias=False, tied=False)
+    desc = make_desc(preset, max_seq, max(args.batch, 1))
+    gpu = B.GpuOnlyInference(desc, None, feeder=lambda up: random_model(preset, "Q8_0", max_seq, seed=args.seed, upload=up))
+    V = s["vocab"]
+    rng = np.random.default_rng(args.seed + 1)
+    out = {"path": gpu.path()}
+    if args.prefill_len:
+        toks = [int(t) for t in rng.integers(0, V, args.prefill_len)]
+
+        def one():
+            gpu.reset(0)
+            gpu.forward_batch(toks, 0)
+        out["prefill_tok_s"] = args.prefill_len / timed(one, 2, 4)
+    for nb, key in ((1, "decode_b1_tok_s"), (args.batch, "decode_b%d_tok_s" % args.batch)):
+        if nb < 1:
+            continue
+        for q in range(nb):
+            gpu.reset(q)
+            gpu.forward_batch([int(t) for t in rng.integers(0, V, args.prompt_len)], q)
+        state = {"t": [1] * nb}
+
+        def one():
+            state["t"] = gpu.decode_batch_greedy(list(range(nb)), state["t"])
+        out[key] = nb / timed(one, args.warmup, args.steps)
+    out["weight_bytes_per_token"] = gpu.stats()["weight_bytes_per_token"]
+    gpu.close()
+    return out
+
+
+def main(args):
+    import llama_gguf_b200 as B
+    if B.device_count() == 0:
+        print("bench.py --design lazilorn: no CUDA device", file=sys.stderr)
+        return 2
+    sizes = [x for x in (args.sizes.split(",") if args.sizes else SIZES) if x]
+    max_seq = max(args.prefill_len, args.prompt_len + args.warmup + args.steps + 8) + 8
+    res = {}
+    for name in sizes:
+        s = SIZES[name]
+        cfg = lazilorn_config(s)
+        params = n_params(cfg)
+        # llama layer: 4 w^2 (1 + kv/heads)/2-ish attention + 3 w ffn; pick ffn so that the parameter counts match
+        w, L = s["width"], len(s["pattern"])
+        attn = w * w * 2 + 2 * w * s["kv_heads"] * 128
+        ffn = max(256, int(round(((params - s["vocab"] * w) / L - attn) / (3 * w) / 256)) * 256)
+        r = {"params_without_embedding": params, "layers": s["pattern"], "lazilorn_bf16": bench_lazilorn(cfg, args, max_seq),
+             "llama_q8_0": dict(bench_llama(s, L, ffn, args, max_seq), ffn=ffn)}
+        res[name] = r
+        print(name, json.dumps(r), file=sys.stderr, flush=True)
+    print(json.dumps({"bench": "design", "design": "lazilorn", "unit": "tok/s", "prefill_len": args.prefill_len, "prompt_len": args.prompt_len,
+                      "batch": args.batch, "steps": args.steps, "warmup": args.warmup, "timing": "host wall clock around the library calls",
+                      "dtype": "bf16 (lazilorn) / Q8_0 (llama)", "data": "synthetic", "sizes": res}))
+    return 0

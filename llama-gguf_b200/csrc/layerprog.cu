@@ -16,6 +16,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <vector>
@@ -169,6 +170,165 @@ __global__ void __launch_bounds__(256) lp_gemm_kernel(const T* __restrict__ X, i
     }
 }
 
+// ------------------------------------------------------------------------------------------------ GEMM (tcgen05 / TMEM, bf16)
+// Y[t][n] = epi(alpha * sum_k X[t][k] W[n][k]) for many rows: one CTA of 128 threads per (128 weight rows, TN tokens) tile, the f32
+// accumulator in TMEM (TN columns x 128 lanes).  Per K step of 64 elements (128 bytes of bf16 = one row of a 128-byte swizzle
+// atom) the threads copy the weight rows and the activation rows with 16-byte cp.async into K-major SWIZZLE_128B tiles (chunk c of
+// row r lands at chunk c ^ (r & 7)); TC_STAGES such stages are in flight.  When a stage has landed: fence.proxy.async, barrier,
+// and one thread issues 4 x tcgen05.mma.cta_group::1.kind::f16 (M = 128, N = TN, K = 16, bf16 operands) and commits them to the
+// stage's mbarrier; a stage is refilled when that commit has arrived.  Epilogue: warp w reads TMEM lanes 32w .. 32w + 31 (= weight
+// rows) 32 token columns at a time; a warp's stores of one token are 32 consecutive outputs.  Every mbarrier wait is bounded: a
+// wait that gives up sets *err and the CTA drains its copies, frees its TMEM columns and returns.
+constexpr int TC_M = 128, TC_K = 64, TC_STAGES = 4;
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// K-major SWIZZLE_128B shared-memory matrix descriptor: start >> 4, LBO (unused) = 1, SBO = 1024 bytes between 8-row groups,
+// version 1 at bit 46, layout SWIZZLE_128B = 2 at bit 61
+__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// instruction descriptor: D = f32 (bits 4-5 = 1), A = B = bf16 (1 at bits 7 and 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+__device__ __forceinline__ uint32_t tc_idesc(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok = 0;
+    const long long t0 = clock64();
+    while (!ok) {
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (!ok && clock64() - t0 > 2000000000LL) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ uint32_t tc_sw128(int r, int c) {
+    return (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u + (uint32_t)((c ^ (r & 7)) << 4);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {   // bytes = 16, or 0 for a zero chunk
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+template <int TN, int EPI>
+__global__ void __launch_bounds__(128) lp_gemm_tc_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
+                                                         void* __restrict__ Y, int ldy, int R, int N, int K, float alpha, int* err) {
+    extern __shared__ __align__(1024) uint8_t tc_smem[];
+    __shared__ __align__(8) unsigned long long s_bar[TC_STAGES];
+    __shared__ uint32_t s_tmem;
+    constexpr int kStage = (TC_M + TN) * 128;
+    uint8_t* base = tc_smem + ((1024u - (smem_u32(tc_smem) & 1023u)) & 1023u);   // the swizzle is on absolute address bits
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int n0 = blockIdx.x * TC_M, t0 = blockIdx.y * TN;
+    const uint32_t bar = smem_u32(&s_bar[0]);
+    constexpr int kCols = TN < 32 ? 32 : TN;
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < TC_STAGES; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar + 8u * i) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "n"(kCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    const uint32_t idesc = tc_idesc(TC_M, TN);
+    const int steps = (K + TC_K - 1) / TC_K;
+    // copies of K step `st` into its stage: 8 chunks per row, (128 + TN) rows, spread over the 128 threads
+    auto load = [&](int st) {
+        uint8_t* tA = base + (st % TC_STAGES) * kStage;
+        uint8_t* tB = tA + TC_M * 128;
+        const int k0 = st * TC_K;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int i = tid + u * 128, r = i >> 3, c = i & 7, n = n0 + r, k = k0 + 8 * c;
+            const bool in = n < N && k < K;
+            cp_async16(smem_u32(tA + tc_sw128(r, c)), in ? (const void*)(W + (size_t)n * ldw + k) : (const void*)W, in ? 16u : 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < TN / 16; u++) {
+            const int i = tid + u * 128, r = i >> 3, c = i & 7, t = t0 + r, k = k0 + 8 * c;
+            const bool in = t < R && k < K;
+            cp_async16(smem_u32(tB + tc_sw128(r, c)), in ? (const void*)(X + (size_t)t * ldx + k) : (const void*)X, in ? 16u : 0u);
+        }
+    };
+    for (int st = 0; st < TC_STAGES - 1; st++) {
+        if (st < steps) load(st);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    bool alive = true;
+    for (int it = 0; it < steps; it++) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(TC_STAGES - 2) : "memory");   // this thread's copies of step `it` have landed
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");               // generic-proxy writes -> visible to the tensor core
+        __syncthreads();
+        if (tid == 0 && alive) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint8_t* tA = base + (it % TC_STAGES) * kStage;
+            const uint64_t da = tc_desc(smem_u32(tA)), db = tc_desc(smem_u32(tA + TC_M * 128));
+#pragma unroll
+            for (int kk = 0; kk < TC_K / 16; kk++) {   // 16 bf16 = 32 bytes along the swizzled row: start address + 2
+                const uint32_t accum = (it > 0 || kk > 0) ? 1u : 0u;
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem),
+                    "l"(da + (uint64_t)(2 * kk)), "l"(db + (uint64_t)(2 * kk)), "r"(idesc), "r"(accum)
+                    : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar + 8u * (it % TC_STAGES)) : "memory");
+        }
+        // refill the stage that step it - 1 read: its MMAs must be done (they run while the MMAs of step `it` wait in the queue)
+        const int nx = it + TC_STAGES - 1;
+        if (nx < steps) {
+            if (it >= 1 && alive) {
+                const int ps = (it - 1) % TC_STAGES;
+                if (!tc_wait(bar + 8u * ps, (uint32_t)(((it - 1) / TC_STAGES) & 1))) {
+                    alive = false;
+                    if (err) atomicExch(err, 1);
+                }
+            }
+            if (alive) load(nx);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (alive && steps > 0 && !tc_wait(bar + 8u * ((steps - 1) % TC_STAGES), (uint32_t)(((steps - 1) / TC_STAGES) & 1))) {
+        alive = false;
+        if (err) atomicExch(err, 2);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int n = n0 + tid;
+    if (alive) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < TN; c0 += 32) {
+            if (t0 + c0 >= R) break;   // CTA-uniform
+            uint32_t v[32];
+            const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                  "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                  "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                  "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                : "r"(taddr));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (n < N) {
+#pragma unroll
+                for (int c = 0; c < 32; c++) {
+                    const int t = t0 + c0 + c;
+                    if (t < R) epi_store<bf16, EPI>(Y, (size_t)t * ldy + n, alpha * __uint_as_float(v[c]));
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kCols) : "memory");
+}
+
 // Few rows (decoding): one warp per output column, the weight row is read once with 16-byte loads and meets up to GV_ROWS
 // activation rows; W streams from HBM at the copy rate, the activations come out of L1/L2.
 constexpr int GV_ROWS = 8;
@@ -268,83 +428,105 @@ __global__ void lp_attn_prep_kernel(StepMeta sm, AttnGeom a, const float* __rest
     for (int c = threadIdx.x; c < a.G * a.vdim; c += blockDim.x) vc[c] = p[a.v_off + c];
 }
 
-// One warp per (row, query head): keys in blocks of 32, one key per lane for the scores (q from shared memory), online softmax in
-// f32, then the 32 value rows are added lane-per-channel.  Visible keys of position i: [0, min(keep_first, lo)) and [lo, i],
-// lo = max(0, i - window + 1).  The output is multiplied by sigmoid(gate) when the layer has an output gate.
+// One block of ATT_WARPS warps per (row, query head).  Keys go in blocks of 32, dealt to the warps in turn: one key per lane for the
+// scores (q from shared memory), online softmax in f32 per warp, then the block's 32 value rows are added lane-per-channel; the
+// warps' partial (max, sum, output) triples are merged through shared memory.  Visible keys of position i: [0, min(keep_first, lo))
+// and [lo, i], lo = max(0, i - window + 1).  The output is multiplied by sigmoid(gate) when the layer has an output gate.
 constexpr int ATT_ACC = 16;   // value channels per lane: vdim <= 512
+constexpr int ATT_WARPS = 4;
 template <typename OutT>
-__global__ void __launch_bounds__(128) lp_window_attn_kernel(StepMeta sm, AttnGeom a, const float* __restrict__ qbuf, const float* __restrict__ P,
-                                                             int ldp, OutT* __restrict__ out) {
+__global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta sm, AttnGeom a, const float* __restrict__ qbuf,
+                                                                        const float* __restrict__ P, int ldp, OutT* __restrict__ out) {
     extern __shared__ float smem[];
-    const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.y * (blockDim.x >> 5) + warp;
-    if (h >= a.H) return;
-    float* qs = smem + warp * a.dim;
+    float* qs = smem;                                  // [dim]
+    float* acc_s = smem + ((a.dim + 3) & ~3);          // [ATT_WARPS][vdim]
+    float* ml_s = acc_s + ATT_WARPS * a.vdim;          // [ATT_WARPS][2]
+    const int r = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int run = sm.row_run[r], i = sm.row_pos[r];
     const int g = h / (a.H / a.G);
     const float* q = qbuf + (size_t)r * a.H * a.dim + h * a.dim;
-    for (int d = lane; d < a.dim; d += 32) qs[d] = q[d];
-    __syncwarp();
+    for (int d = threadIdx.x; d < a.dim; d += blockDim.x) qs[d] = q[d];
+    __syncthreads();
     const float* kc = reinterpret_cast<const float*>(sm.run_kv[run] + a.kv_off);
     const float* vc = kc + (size_t)a.cap * a.G * a.dim;
     const int ldk = a.G * a.dim, ldv = a.G * a.vdim;
     const int lo = max(0, i - a.window + 1);
     const int a_end = min(a.keep_first, lo);
+    const int nb0 = (a_end + 31) >> 5, nb1 = (i + 1 - lo + 31) >> 5;
     float m = -INFINITY, l = 0.0f;
     float acc[ATT_ACC];
 #pragma unroll
     for (int c = 0; c < ATT_ACC; c++) acc[c] = 0.0f;
     const bool v4 = (a.dim & 3) == 0;
-    for (int part = 0; part < 2; part++) {
-        const int beg = part ? lo : 0, end = part ? i + 1 : a_end;
-        for (int j0 = beg; j0 < end; j0 += 32) {
-            const int j = j0 + lane;
-            float s = -INFINITY;
-            if (j < end) {
-                const float* kr = kc + (size_t)j * ldk + g * a.dim;
-                float d0 = 0.0f;
-                if (v4) {
-                    for (int d = 0; d < a.dim; d += 4) {
-                        const float4 kv = *reinterpret_cast<const float4*>(kr + d);
-                        d0 = fmaf(qs[d], kv.x, d0);
-                        d0 = fmaf(qs[d + 1], kv.y, d0);
-                        d0 = fmaf(qs[d + 2], kv.z, d0);
-                        d0 = fmaf(qs[d + 3], kv.w, d0);
-                    }
-                } else {
-                    for (int d = 0; d < a.dim; d++) d0 = fmaf(qs[d], kr[d], d0);
+    for (int b = warp; b < nb0 + nb1; b += ATT_WARPS) {
+        const int j0 = b < nb0 ? b * 32 : lo + (b - nb0) * 32;
+        const int end = b < nb0 ? a_end : i + 1;
+        const int j = j0 + lane;
+        float s = -INFINITY;
+        if (j < end) {
+            const float* kr = kc + (size_t)j * ldk + g * a.dim;
+            float d0 = 0.0f, d1 = 0.0f;
+            if (v4) {
+#pragma unroll 4
+                for (int d = 0; d < a.dim; d += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+                    d0 = fmaf(qs[d], kv.x, d0);
+                    d1 = fmaf(qs[d + 1], kv.y, d1);
+                    d0 = fmaf(qs[d + 2], kv.z, d0);
+                    d1 = fmaf(qs[d + 3], kv.w, d1);
                 }
-                s = d0 * a.scale;
+            } else {
+                for (int d = 0; d < a.dim; d++) d0 = fmaf(qs[d], kr[d], d0);
             }
-            const float m_new = fmaxf(m, wmax(s));
-            const float p = j < end ? expf(s - m_new) : 0.0f;
-            const float corr = expf(m - m_new);      // (m = -inf on the first block: 0)
-            l = l * corr + wsum(p);
-            m = m_new;
+            s = (d0 + d1) * a.scale;
+        }
+        const float m_new = fmaxf(m, wmax(s));
+        const float p = j < end ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m - m_new);      // (m = -inf on the warp's first block: 0)
+        l = l * corr + wsum(p);
+        m = m_new;
 #pragma unroll
-            for (int c = 0; c < ATT_ACC; c++) acc[c] *= corr;
-            const int cnt = min(32, end - j0);
-            for (int jj = 0; jj < cnt; jj++) {
-                const float pj = __shfl_sync(0xffffffffu, p, jj);
-                const float* vr = vc + (size_t)(j0 + jj) * ldv + g * a.vdim;
+        for (int c = 0; c < ATT_ACC; c++) acc[c] *= corr;
+        const int cnt = min(32, end - j0);
+#pragma unroll 4
+        for (int jj = 0; jj < cnt; jj++) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const float* vr = vc + (size_t)(j0 + jj) * ldv + g * a.vdim;
 #pragma unroll
-                for (int c = 0; c < ATT_ACC; c++) {
-                    const int ch = c * 32 + lane;
-                    if (ch < a.vdim) acc[c] = fmaf(pj, vr[ch], acc[c]);
-                }
+            for (int c = 0; c < ATT_ACC; c++) {
+                const int ch = c * 32 + lane;
+                if (ch < a.vdim) acc[c] = fmaf(pj, vr[ch], acc[c]);
             }
         }
     }
-    const float invl = 1.0f / l;
-    const float* gate = P + (size_t)r * ldp + a.g_off + h * a.vdim;
 #pragma unroll
     for (int c = 0; c < ATT_ACC; c++) {
         const int ch = c * 32 + lane;
-        if (ch < a.vdim) {
-            float o = acc[c] * invl;
-            if (a.out_gate) o *= sigmoid_f(gate[ch]);
-            out[(size_t)r * a.H * a.vdim + h * a.vdim + ch] = from_f<OutT>(o);
-        }
+        if (ch < a.vdim) acc_s[warp * a.vdim + ch] = acc[c];
+    }
+    if (lane == 0) {
+        ml_s[2 * warp] = m;
+        ml_s[2 * warp + 1] = l;
+    }
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; w++) M = fmaxf(M, ml_s[2 * w]);
+    float wgt[ATT_WARPS], lsum = 0.0f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; w++) {
+        wgt[w] = expf(ml_s[2 * w] - M);           // a warp without keys: exp(-inf) = 0
+        lsum = fmaf(ml_s[2 * w + 1], wgt[w], lsum);
+    }
+    const float invl = 1.0f / lsum;
+    const float* gate = P + (size_t)r * ldp + a.g_off + h * a.vdim;
+    for (int ch = threadIdx.x; ch < a.vdim; ch += blockDim.x) {
+        float o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) o = fmaf(acc_s[w * a.vdim + ch], wgt[w], o);
+        o *= invl;
+        if (a.out_gate) o *= sigmoid_f(gate[ch]);
+        out[(size_t)r * a.H * a.vdim + h * a.vdim + ch] = from_f<OutT>(o);
     }
 }
 
@@ -360,13 +542,20 @@ struct MemGeom {
     size_t rec_off;
 };
 constexpr int SCAN_BD = 64;
+// Tokens are staged into shared memory SCAN_CH at a time (coalesced loads, gates and unit norms worked out one token per thread), so
+// the serial loop over a chunk's tokens runs out of shared memory and registers: one global round trip per chunk instead of three
+// per token.
+template <int DMAX> struct ScanChunk { static constexpr int N = DMAX > 128 ? 8 : 32; };
 template <int DMAX>
 __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, MemGeom g, const float* __restrict__ P, int ldp,
                                                                    const float* __restrict__ ib, const float* __restrict__ fb,
                                                                    float* __restrict__ O, int ldo) {
-    __shared__ float qs[2][DMAX], ks[2][DMAX], ns[DMAX];
-    const int j = blockIdx.x * SCAN_BD + threadIdx.x, h = blockIdx.y, run = blockIdx.z;
-    const int lane = threadIdx.x & 31;
+    constexpr int CH = ScanChunk<DMAX>::N;
+    __shared__ __align__(16) float qs[CH][DMAX];
+    __shared__ __align__(16) float ks[CH][DMAX];
+    __shared__ float vs[CH][SCAN_BD], il_s[CH], fl_s[CH];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int j = blockIdx.x * SCAN_BD + tid, h = blockIdx.y, run = blockIdx.z;
     const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
     float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
     float* ng = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim + (size_t)h * g.dim;
@@ -375,50 +564,74 @@ __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, 
     float s[DMAX];
 #pragma unroll
     for (int d = 0; d < DMAX; d++) s[d] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
-    for (int d = threadIdx.x; d < DMAX; d += SCAN_BD) {
-        ns[d] = d < g.dim ? ng[d] : 0.0f;
-        qs[0][d] = qs[1][d] = ks[0][d] = ks[1][d] = 0.0f;
+    float nreg[DMAX / 32];   // n, element lane + 32 i (every warp keeps its own copy)
+#pragma unroll
+    for (int i = 0; i < DMAX / 32; i++) nreg[i] = lane + 32 * i < g.dim ? ng[lane + 32 * i] : 0.0f;
+    for (int i = tid; i < CH * DMAX; i += SCAN_BD) {   // the padding beyond dim stays zero
+        (&qs[0][0])[i] = 0.0f;
+        (&ks[0][0])[i] = 0.0f;
     }
     float m = *mg;
     const float qscale = 1.0f / sqrtf((float)g.dim);
     const float bi = ib[h], bf_ = fb[h];
-    __syncthreads();
-    for (int r = r0; r < r1; r++) {
-        const int b = (r - r0) & 1;
-        const float* p = P + (size_t)r * ldp;
-        for (int d = threadIdx.x; d < g.dim; d += SCAN_BD) {
-            qs[b][d] = p[g.q_off + h * g.dim + d] * qscale;
-            ks[b][d] = p[g.k_off + h * g.dim + d];
+    for (int c0 = r0; c0 < r1; c0 += CH) {
+        const int nt = min(CH, r1 - c0);
+        __syncthreads();   // the previous chunk has been consumed
+        for (int i = tid; i < nt * g.dim; i += SCAN_BD) {
+            const int t = i / g.dim, d = i - t * g.dim;
+            const float* p = P + (size_t)(c0 + t) * ldp;
+            qs[t][d] = p[g.q_off + h * g.dim + d] * qscale;
+            ks[t][d] = p[g.k_off + h * g.dim + d];
         }
-        const float il = g.cap * tanhf((p[g.i_off + h] + bi) / g.cap);
-        const float fl = logsigmoid_f(g.cap * tanhf((p[g.f_off + h] + bf_) / g.cap));
-        const float v = live ? p[g.v_off + h * g.vdim + j] : 0.0f;
-        const float m_new = fmaxf(fl + m, il);
-        const float fa = expf(fl + m - m_new), ia = expf(il - m_new);
-        m = m_new;
-        __syncthreads();                                   // q, k of this token are in place; everyone is done with token r - 1
-        for (int d = threadIdx.x; d < g.dim; d += SCAN_BD) ns[d] = fa * ns[d] + ia * ks[b][d];
-        float acc = 0.0f;
-        const float iv = ia * v;
+        for (int i = tid; i < nt * SCAN_BD; i += SCAN_BD) {
+            const int t = i / SCAN_BD;
+            vs[t][tid] = live ? P[(size_t)(c0 + t) * ldp + g.v_off + h * g.vdim + j] : 0.0f;
+        }
+        if (tid < nt) {
+            const float* p = P + (size_t)(c0 + tid) * ldp;
+            il_s[tid] = g.cap * tanhf((p[g.i_off + h] + bi) / g.cap);
+            fl_s[tid] = logsigmoid_f(g.cap * tanhf((p[g.f_off + h] + bf_) / g.cap));
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; t++) {
+            const float il = il_s[t], fl = fl_s[t];
+            const float m_new = fmaxf(fl + m, il);
+            const float fa = expf(fl + m - m_new), ia = expf(il - m_new);
+            m = m_new;
+            const float iv = ia * vs[t][tid];
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-        for (int d = 0; d < DMAX; d++) {
-            s[d] = fmaf(fa, s[d], ks[b][d] * iv);
-            acc = fmaf(s[d], qs[b][d], acc);
+            for (int d = 0; d < DMAX; d += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][d]);
+                s[d] = fmaf(fa, s[d], k4.x * iv);
+                s[d + 1] = fmaf(fa, s[d + 1], k4.y * iv);
+                s[d + 2] = fmaf(fa, s[d + 2], k4.z * iv);
+                s[d + 3] = fmaf(fa, s[d + 3], k4.w * iv);
+                a0 = fmaf(s[d], q4.x, a0);
+                a1 = fmaf(s[d + 1], q4.y, a1);
+                a2 = fmaf(s[d + 2], q4.z, a2);
+                a3 = fmaf(s[d + 3], q4.w, a3);
+            }
+            float nq = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DMAX / 32; i++) {
+                nreg[i] = fmaf(fa, nreg[i], ia * ks[t][lane + 32 * i]);
+                nq = fmaf(nreg[i], qs[t][lane + 32 * i], nq);
+            }
+            nq = wsum(nq);
+            if (live) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = ((a0 + a1) + (a2 + a3)) / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
         }
-        __syncthreads();                                   // n of this token is in place
-        float nq = 0.0f;
-        for (int d = lane; d < g.dim; d += 32) nq = fmaf(ns[d], qs[b][d], nq);
-        nq = wsum(nq);
-        if (live) O[(size_t)r * ldo + h * g.vdim + j] = acc / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
     }
-    __syncthreads();
     if (live)
 #pragma unroll
         for (int d = 0; d < DMAX; d++)
             if (d < g.dim) Sg[(size_t)d * g.vdim + j] = s[d];
-    if (blockIdx.x == 0) {
-        for (int d = threadIdx.x; d < g.dim; d += SCAN_BD) ng[d] = ns[d];
-        if (threadIdx.x == 0) *mg = m;
+    if (blockIdx.x == 0 && tid < 32) {
+#pragma unroll
+        for (int i = 0; i < DMAX / 32; i++)
+            if (lane + 32 * i < g.dim) ng[lane + 32 * i] = nreg[i];
+        if (tid == 0) *mg = m;
     }
 }
 
@@ -460,13 +673,17 @@ __global__ void lp_conv_tail_kernel(StepMeta sm, DeltaGeom g, const float* __res
 // Per (run, head): thread = value channel j with S[:, j] in registers.  q, k become unit vectors (x / sqrt(sum x^2 + 1e-6), q also
 // times dim^(-1/2)); beta = sigmoid(zb); decay = exp(-exp(A_log) softplus(za + dt_bias));
 //   S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q   (the read-out sees this token's write).
+// Chunks of tokens are staged as in the matrix-memory kernel: a warp normalises q and k of one token at a time.
 template <int DMAX>
 __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, DeltaGeom g, const float* __restrict__ QKV, const float* __restrict__ P,
                                                                  int ldp, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                                                                  float* __restrict__ O, int ldo) {
-    __shared__ float qs[2][DMAX], ks[2][DMAX];
-    const int j = blockIdx.x * SCAN_BD + threadIdx.x, h = blockIdx.y, run = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int CH = ScanChunk<DMAX>::N;
+    __shared__ __align__(16) float qs[CH][DMAX];
+    __shared__ __align__(16) float ks[CH][DMAX];
+    __shared__ float vs[CH][SCAN_BD], beta_s[CH], dec_s[CH];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int j = blockIdx.x * SCAN_BD + tid, h = blockIdx.y, run = blockIdx.z;
     const int hk = h / (g.H / g.G);
     const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
     float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
@@ -474,42 +691,68 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
     float s[DMAX];
 #pragma unroll
     for (int d = 0; d < DMAX; d++) s[d] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
-    for (int d = threadIdx.x; d < DMAX; d += SCAN_BD) qs[0][d] = qs[1][d] = ks[0][d] = ks[1][d] = 0.0f;
+    for (int i = tid; i < CH * DMAX; i += SCAN_BD) {
+        (&qs[0][0])[i] = 0.0f;
+        (&ks[0][0])[i] = 0.0f;
+    }
     const float rate = expf(A_log[h]), dtb = dt_bias[h];
     const float qscale = 1.0f / sqrtf((float)g.dim);
     const int k_col = g.G * g.dim, v_col = 2 * g.G * g.dim;
-    __syncthreads();
-    for (int r = r0; r < r1; r++) {
-        const int b = (r - r0) & 1;
-        const float* x = QKV + (size_t)r * g.C;
-        if (warp < 2) {   // warp 0: q, warp 1: k
-            const float* src = x + (warp ? k_col : 0) + hk * g.dim;
+    for (int c0 = r0; c0 < r1; c0 += CH) {
+        const int nt = min(CH, r1 - c0);
+        __syncthreads();
+        for (int t = warp; t < 2 * nt; t += SCAN_BD / 32) {   // (token, q or k) pairs, one per warp at a time
+            const int tt = t >> 1, isk = t & 1;
+            const float* src = QKV + (size_t)(c0 + tt) * g.C + (isk ? k_col : 0) + hk * g.dim;
             float ss = 0.0f;
             for (int d = lane; d < g.dim; d += 32) ss += src[d] * src[d];
             ss = wsum(ss);
-            const float inv = (warp ? 1.0f : qscale) / sqrtf(ss + 1e-6f);
-            float* dst = warp ? ks[b] : qs[b];
+            const float inv = (isk ? 1.0f : qscale) / sqrtf(ss + 1e-6f);
+            float* dst = isk ? ks[tt] : qs[tt];
             for (int d = lane; d < g.dim; d += 32) dst[d] = src[d] * inv;
         }
-        const float* p = P + (size_t)r * ldp;
-        const float beta = sigmoid_f(p[g.b_off + h]);
-        const float decay = expf(-rate * softplus_f(p[g.a_off + h] + dtb));
-        const float v = live ? x[v_col + h * g.vdim + j] : 0.0f;
+        for (int i = tid; i < nt * SCAN_BD; i += SCAN_BD) {
+            const int t = i / SCAN_BD;
+            vs[t][tid] = live ? QKV[(size_t)(c0 + t) * g.C + v_col + h * g.vdim + j] : 0.0f;
+        }
+        if (tid < nt) {
+            const float* p = P + (size_t)(c0 + tid) * ldp;
+            beta_s[tid] = sigmoid_f(p[g.b_off + h]);
+            dec_s[tid] = expf(-rate * softplus_f(p[g.a_off + h] + dtb));
+        }
         __syncthreads();
-        float kd = 0.0f;
+        for (int t = 0; t < nt; t++) {
+            const float decay = dec_s[t], beta = beta_s[t], v = vs[t][tid];
+            float k0 = 0.0f, k1 = 0.0f, k2 = 0.0f, k3 = 0.0f;
 #pragma unroll
-        for (int d = 0; d < DMAX; d++) {
-            s[d] *= decay;
-            kd = fmaf(s[d], ks[b][d], kd);
-        }
-        const float u = beta * (v - kd);
-        float acc = 0.0f;
+            for (int d = 0; d < DMAX; d += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d]);
+                s[d] *= decay;
+                s[d + 1] *= decay;
+                s[d + 2] *= decay;
+                s[d + 3] *= decay;
+                k0 = fmaf(s[d], k4.x, k0);
+                k1 = fmaf(s[d + 1], k4.y, k1);
+                k2 = fmaf(s[d + 2], k4.z, k2);
+                k3 = fmaf(s[d + 3], k4.w, k3);
+            }
+            const float u = beta * (v - ((k0 + k1) + (k2 + k3)));
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-        for (int d = 0; d < DMAX; d++) {
-            s[d] = fmaf(ks[b][d], u, s[d]);
-            acc = fmaf(s[d], qs[b][d], acc);
+            for (int d = 0; d < DMAX; d += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][d]);
+                s[d] = fmaf(k4.x, u, s[d]);
+                s[d + 1] = fmaf(k4.y, u, s[d + 1]);
+                s[d + 2] = fmaf(k4.z, u, s[d + 2]);
+                s[d + 3] = fmaf(k4.w, u, s[d + 3]);
+                a0 = fmaf(s[d], q4.x, a0);
+                a1 = fmaf(s[d + 1], q4.y, a1);
+                a2 = fmaf(s[d + 2], q4.z, a2);
+                a3 = fmaf(s[d + 3], q4.w, a3);
+            }
+            if (live) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = (a0 + a1) + (a2 + a3);
         }
-        if (live) O[(size_t)r * ldo + h * g.vdim + j] = acc;
     }
     if (live)
 #pragma unroll
@@ -621,6 +864,17 @@ struct LpModel {
     size_t taps_floats = 0;
     int taps_len = 0;
     uint64_t launches = 0, weight_bytes = 0, kv_bytes_per_pos = 0;
+    // tensor-core GEMM: on for bf16 steps of at least tc_min_rows rows (B200_LP_TC=0 keeps the CUDA-core kernel); *tc_err is set by a
+    // bounded wait that gave up
+    bool use_tc = true;
+    // decode steps replay a CUDA graph per (rows, wanted rows, head); a graph is void once a scratch buffer has moved (B200_LP_GRAPH=0: eager)
+    struct Graph { cudaGraphExec_t exec = nullptr; uint64_t launches = 0, epoch = 0; bool warm = false; };
+    std::map<uint64_t, Graph> graphs;
+    uint64_t scratch_epoch = 1;
+    bool use_graph = true;
+    int tc_min_rows = 17;
+    int* tc_err = nullptr;
+    int* h_tc_err = nullptr;
 };
 
 namespace {
@@ -698,6 +952,45 @@ void launch(LpModel* m, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sm
     m->launches++;
 }
 
+// The tensor-core GEMM takes bf16 operands whose rows are 16-byte aligned (K and the row pitches multiples of 8).
+template <int TN>
+bool tc_launch(LpModel* m, const bf16* x, int ldx, const bf16* w, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
+    const size_t smem = (size_t)TC_STAGES * (TC_M + TN) * 128 + 1024;
+    static bool once[3][64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto prep = [&](auto kern, int e) {
+        if (dev >= 0 && dev < 64 && once[e][dev]) return true;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        if (dev >= 0 && dev < 64) once[e][dev] = true;
+        return true;
+    };
+    dim3 grid((N + TC_M - 1) / TC_M, (R + TN - 1) / TN), block(128);
+    if (epi == EPI_STORE) {
+        if (!prep(lp_gemm_tc_kernel<TN, EPI_STORE>, 0)) return false;
+        launch(m, lp_gemm_tc_kernel<TN, EPI_STORE>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, m->tc_err);
+    } else if (epi == EPI_ADD) {
+        if (!prep(lp_gemm_tc_kernel<TN, EPI_ADD>, 1)) return false;
+        launch(m, lp_gemm_tc_kernel<TN, EPI_ADD>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, m->tc_err);
+    } else {
+        if (!prep(lp_gemm_tc_kernel<TN, EPI_RELU2>, 2)) return false;
+        launch(m, lp_gemm_tc_kernel<TN, EPI_RELU2>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, m->tc_err);
+    }
+    return true;
+}
+bool tc_gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
+    if (m->f32 || !m->use_tc || R < m->tc_min_rows) return false;
+    if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return false;
+    const bf16* x = (const bf16*)X;
+    const bf16* w = (const bf16*)W;
+    if (R <= 64) return tc_launch<64>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);
+    if (R <= 128 || (long long)((N + TC_M - 1) / TC_M) * ((R + 255) / 256) < 148) return tc_launch<128>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);
+    return tc_launch<256>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);
+}
+
 // Y = epi(alpha X W^T): rows of the step against a [N][K] matrix in the compute type
 template <typename T>
 void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
@@ -712,6 +1005,7 @@ void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int N, int K, voi
         else launch(m, lp_gemv_kernel<T, EPI_RELU2>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok);
         return;
     }
+    if (tc_gemm(m, X, ldx, W, N, K, Y, ldy, R, alpha, epi)) return;
     dim3 grid((N + GB - 1) / GB, (R + GB - 1) / GB), block(256);
     if (epi == EPI_STORE) launch(m, lp_gemm_kernel<T, EPI_STORE>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha);
     else if (epi == EPI_ADD) launch(m, lp_gemm_kernel<T, EPI_ADD>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha);
@@ -780,6 +1074,14 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
         for (int i = 0; i < p.n_layers; i++) push(i, -1);
     }
     m->slot.resize(p.max_batch);
+    {
+        const char* e = getenv("B200_LP_TC");
+        if (e && *e) m->use_tc = atoi(e) != 0;
+        e = getenv("B200_LP_GRAPH");
+        if (e && *e) m->use_graph = atoi(e) != 0;
+        e = getenv("B200_LP_TC_MIN_ROWS");
+        if (e && *e) m->tc_min_rows = std::max(1, atoi(e));
+    }
     *out = m;
     return B200_OK;
 }
@@ -997,6 +1299,10 @@ int lp_finalize(LpModel* m, std::string* err) {
         LCU_ALLOC(cudaMalloc((void**)&m->inv_freq, up16(nf * sizeof(double))));
         LCU(cudaMemcpy(m->inv_freq, f.data(), nf * sizeof(double), cudaMemcpyHostToDevice));
     }
+    LCU_ALLOC(cudaMalloc((void**)&m->tc_err, 256));
+    LCU(cudaMemset(m->tc_err, 0, 256));
+    LCU_ALLOC(cudaHostAlloc((void**)&m->h_tc_err, 64, cudaHostAllocDefault));
+    *m->h_tc_err = 0;
     m->finalized = true;
     return B200_OK;
 }
@@ -1006,6 +1312,8 @@ void lp_destroy(LpModel* m) {
     cudaSetDevice(m->device);
     cudaStreamSynchronize(m->stream);
     for (auto& kv : m->tensors) cudaFree(kv.second.d);
+    for (auto& g : m->graphs)
+        if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     for (LayerPlan& L : m->plan) cudaFree(L.w_in);
     for (SlotMem& s : m->slot) { cudaFree(s.kv); cudaFree(s.rec); }
     for (SlotMem& s : m->pool) { cudaFree(s.kv); cudaFree(s.rec); }
@@ -1014,6 +1322,8 @@ void lp_destroy(LpModel* m) {
         cudaFree(ptr);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_logits) cudaFreeHost(m->h_logits);
+    if (m->h_tc_err) cudaFreeHost(m->h_tc_err);
+    cudaFree(m->tc_err);
     delete m;
 }
 
@@ -1062,6 +1372,7 @@ int grow(P** ptr, size_t bytes, std::string* err) {
 
 int ensure_scratch(LpModel* m, int R, int n_runs, int n_want, std::string* err) {
     int rc;
+    if (R > m->cap_rows || n_want > m->cap_want || n_runs > m->cap_runs) m->scratch_epoch++;   // buffers or table offsets move: graphs are void
     const size_t es = elt(m);
     const int W = m->p.width;
     if (R > m->cap_rows) {
@@ -1093,6 +1404,75 @@ int ensure_scratch(LpModel* m, int R, int n_runs, int n_want, std::string* err) 
         m->meta_bytes = meta;
     }
     return B200_OK;
+}
+
+// Every kernel of one step, in order, on the model's stream: eagerly, or while the stream is being captured into a CUDA graph (a
+// decode step: one row per run, nothing allocated).  head: 0 = no logits, 1 = logits of the wanted rows, 2 = their greedy picks.
+void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want, int head, int taps_len) {
+    const b200_program_desc& p = m->p;
+    const int W = p.width;
+    const float* loop_step = p.loop_stop > p.loop_start ? (const float*)find(m, "loop.step")->d : nullptr;
+    // embedding
+    if (m->f32) launch(m, lp_embed_kernel<float>, dim3(R), dim3(128), 0, sm, (const float*)find(m, "embed")->d, m->inv_freq, m->x, W, p.embed_scale, p.pos_sinusoid);
+    else launch(m, lp_embed_kernel<bf16>, dim3(R), dim3(128), 0, sm, (const bf16*)find(m, "embed")->d, m->inv_freq, m->x, W, p.embed_scale, p.pos_sinusoid);
+    for (size_t run = 0; run < m->runs.size(); run++) {
+        LayerPlan& L = m->plan[m->runs[run]];
+        const float* add = m->run_pass[run] >= 0 ? loop_step + (size_t)m->run_pass[run] * W : nullptr;
+        rmsnorm(m, m->x, add, L.norm1, m->hn, nullptr, R);
+        gemm(m, m->hn, W, L.w_in, L.n_in, W, m->P, L.n_in, R, 1.0f, EPI_STORE);
+        if (L.d.mixer == B200_MIX_WINDOW_MEMORY) {
+            AttnGeom ag = L.ag;
+            ag.kv_off = m->run_kv_off[run];
+            launch(m, lp_attn_prep_kernel, dim3(R), dim3(128), 0, sm, ag, (const float*)m->P, L.n_in, L.qn, L.kn, m->qbuf);
+            dim3 agrid(R, ag.H);
+            const size_t asmem = (size_t)(((ag.dim + 3) & ~3) + ATT_WARPS * ag.vdim + 2 * ATT_WARPS) * 4;
+            if (m->f32) launch(m, lp_window_attn_kernel<float>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (float*)m->act_a);
+            else launch(m, lp_window_attn_kernel<bf16>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (bf16*)m->act_a);
+            MemGeom mg = L.mg;
+            mg.rec_off = m->run_rec_off[run];
+            const int ldo = mg.H * mg.vdim;
+            dim3 sgrid((mg.vdim + SCAN_BD - 1) / SCAN_BD, mg.H, n_runs);
+            switch (pick_dmax(mg.dim)) {
+                case 32: launch(m, lp_matrix_memory_kernel<32>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
+                case 64: launch(m, lp_matrix_memory_kernel<64>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
+                case 128: launch(m, lp_matrix_memory_kernel<128>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
+                default: launch(m, lp_matrix_memory_kernel<256>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
+            }
+            dim3 hgrid(R, (mg.H + 3) / 4);
+            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (float*)m->act_b, R);
+            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (bf16*)m->act_b, R);
+            gemm(m, m->act_a, ag.H * ag.vdim, L.wo_attn, W, ag.H * ag.vdim, m->x, W, R, L.d.attn_scale, EPI_ADD);
+            gemm(m, m->act_b, ldo, L.wo_mem, W, ldo, m->x, W, R, L.d.mem_scale, EPI_ADD);
+        } else {
+            DeltaGeom dg = L.dg;
+            dg.rec_off = m->run_rec_off[run];
+            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, m->conv);
+            if (dg.taps > 1) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
+            const int ldo = dg.H * dg.vdim;
+            dim3 sgrid((dg.vdim + SCAN_BD - 1) / SCAN_BD, dg.H, n_runs);
+            switch (pick_dmax(dg.dim)) {
+                case 32: launch(m, lp_gated_delta_kernel<32>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
+                case 64: launch(m, lp_gated_delta_kernel<64>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
+                case 128: launch(m, lp_gated_delta_kernel<128>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
+                default: launch(m, lp_gated_delta_kernel<256>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
+            }
+            dim3 hgrid(R, (dg.H + 3) / 4);
+            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (float*)m->act_a, R);
+            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (bf16*)m->act_a, R);
+            gemm(m, m->act_a, ldo, L.wo_delta, W, ldo, m->x, W, R, 1.0f, EPI_ADD);
+        }
+        if (L.d.ff > 0) {
+            rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
+            gemm(m, m->hn, W, L.w_up, L.d.ff, W, m->act_a, L.d.ff, R, 1.0f, EPI_RELU2);
+            gemm(m, m->act_a, L.d.ff, L.w_down, W, L.d.ff, m->x, W, R, 1.0f, EPI_ADD);
+        }
+        if (taps_len > 0) cudaMemcpyAsync(m->taps + run * (size_t)taps_len * W, m->x, (size_t)taps_len * W * 4, cudaMemcpyDeviceToDevice, m->stream);
+    }
+    if (head) {
+        rmsnorm(m, m->x, nullptr, (const float*)find(m, "final.norm")->d, m->hw, sm.want, n_want);
+        gemm(m, m->hw, W, find(m, "head")->d, p.vocab, W, m->logits, p.vocab, n_want, p.logit_scale, EPI_STORE);
+        if (head == 2) launch(m, lp_argmax_kernel, dim3(n_want), dim3(1024), 0, (const float*)m->logits, p.vocab, m->pick);
+    }
 }
 }  // namespace
 
@@ -1181,7 +1561,6 @@ int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int*
         sm.run_rec = sm.run_kv + m->cap_runs;
     }
     const int W = p.width;
-    const float* loop_step = p.loop_stop > p.loop_start ? (const float*)find(m, "loop.step")->d : nullptr;
     if (m->taps_on) {
         const size_t need = (size_t)m->runs.size() * lens[0] * W;
         if (need > m->taps_floats) {
@@ -1190,83 +1569,71 @@ int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int*
         }
         m->taps_len = lens[0];
     }
-    // embedding
-    if (m->f32) launch(m, lp_embed_kernel<float>, dim3(R), dim3(128), 0, sm, (const float*)find(m, "embed")->d, m->inv_freq, m->x, W, p.embed_scale, p.pos_sinusoid);
-    else launch(m, lp_embed_kernel<bf16>, dim3(R), dim3(128), 0, sm, (const bf16*)find(m, "embed")->d, m->inv_freq, m->x, W, p.embed_scale, p.pos_sinusoid);
-    for (size_t run = 0; run < m->runs.size(); run++) {
-        LayerPlan& L = m->plan[m->runs[run]];
-        const float* add = m->run_pass[run] >= 0 ? loop_step + (size_t)m->run_pass[run] * W : nullptr;
-        rmsnorm(m, m->x, add, L.norm1, m->hn, nullptr, R);
-        gemm(m, m->hn, W, L.w_in, L.n_in, W, m->P, L.n_in, R, 1.0f, EPI_STORE);
-        if (L.d.mixer == B200_MIX_WINDOW_MEMORY) {
-            AttnGeom ag = L.ag;
-            ag.kv_off = m->run_kv_off[run];
-            launch(m, lp_attn_prep_kernel, dim3(R), dim3(128), 0, sm, ag, (const float*)m->P, L.n_in, L.qn, L.kn, m->qbuf);
-            const int wpb = 4;
-            dim3 agrid(R, (ag.H + wpb - 1) / wpb);
-            const size_t asmem = (size_t)wpb * ag.dim * 4;
-            if (m->f32) launch(m, lp_window_attn_kernel<float>, agrid, dim3(32 * wpb), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (float*)m->act_a);
-            else launch(m, lp_window_attn_kernel<bf16>, agrid, dim3(32 * wpb), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (bf16*)m->act_a);
-            MemGeom mg = L.mg;
-            mg.rec_off = m->run_rec_off[run];
-            const int ldo = mg.H * mg.vdim;
-            dim3 sgrid((mg.vdim + SCAN_BD - 1) / SCAN_BD, mg.H, n_runs);
-            switch (pick_dmax(mg.dim)) {
-                case 32: launch(m, lp_matrix_memory_kernel<32>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
-                case 64: launch(m, lp_matrix_memory_kernel<64>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
-                case 128: launch(m, lp_matrix_memory_kernel<128>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
-                default: launch(m, lp_matrix_memory_kernel<256>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
-            }
-            dim3 hgrid(R, (mg.H + 3) / 4);
-            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (float*)m->act_b, R);
-            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (bf16*)m->act_b, R);
-            gemm(m, m->act_a, ag.H * ag.vdim, L.wo_attn, W, ag.H * ag.vdim, m->x, W, R, L.d.attn_scale, EPI_ADD);
-            gemm(m, m->act_b, ldo, L.wo_mem, W, ldo, m->x, W, R, L.d.mem_scale, EPI_ADD);
+    const int head = (n_want > 0 && pick_out) ? 2 : (n_want > 0 && logits_out) ? 1 : 0;
+    const int taps_len = m->taps_on ? lens[0] : 0;
+    // A decode step (one row per run, every slot already holds state) always launches the same kernels with the same arguments: the
+    // tables of the step live at fixed device addresses.  It is captured once per (rows, wanted rows, head) into a CUDA graph and
+    // replayed; the first step of a shape runs eagerly (it also warms the kernels up), the second is the capture.
+    bool decode = m->use_graph && !m->taps_on && R == n_runs;
+    for (int i = 0; i < n_runs && decode; i++) decode = pos0[i] > 0;
+    if (decode) {
+        const uint64_t key = ((uint64_t)R << 34) | ((uint64_t)n_want << 4) | (uint64_t)head;
+        LpModel::Graph& g = m->graphs[key];
+        if (g.exec && g.epoch != m->scratch_epoch) {
+            cudaGraphExecDestroy(g.exec);
+            g = LpModel::Graph();
+        }
+        if (g.exec) {
+            LCU(cudaGraphLaunch(g.exec, m->stream));
+            m->launches += g.launches;
+        } else if (!g.warm) {
+            g.warm = true;
+            enqueue_step(m, sm, R, n_runs, n_want, head, 0);
         } else {
-            DeltaGeom dg = L.dg;
-            dg.rec_off = m->run_rec_off[run];
-            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, m->conv);
-            if (dg.taps > 1) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
-            const int ldo = dg.H * dg.vdim;
-            dim3 sgrid((dg.vdim + SCAN_BD - 1) / SCAN_BD, dg.H, n_runs);
-            switch (pick_dmax(dg.dim)) {
-                case 32: launch(m, lp_gated_delta_kernel<32>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
-                case 64: launch(m, lp_gated_delta_kernel<64>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
-                case 128: launch(m, lp_gated_delta_kernel<128>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
-                default: launch(m, lp_gated_delta_kernel<256>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
+            const uint64_t before = m->launches;
+            cudaGraph_t graph = nullptr;
+            LCU(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+            enqueue_step(m, sm, R, n_runs, n_want, head, 0);
+            cudaError_t e = cudaStreamEndCapture(m->stream, &graph);
+            if (e == cudaSuccess) e = cudaGraphInstantiate(&g.exec, graph, 0);
+            if (graph) cudaGraphDestroy(graph);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                g = LpModel::Graph();
+                m->use_graph = false;          // fall back to eager launches for good
+                m->launches = before;
+                enqueue_step(m, sm, R, n_runs, n_want, head, 0);
+            } else {
+                g.launches = m->launches - before;
+                g.epoch = m->scratch_epoch;
+                LCU(cudaGraphLaunch(g.exec, m->stream));
             }
-            dim3 hgrid(R, (dg.H + 3) / 4);
-            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (float*)m->act_a, R);
-            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (bf16*)m->act_a, R);
-            gemm(m, m->act_a, ldo, L.wo_delta, W, ldo, m->x, W, R, 1.0f, EPI_ADD);
         }
-        if (L.d.ff > 0) {
-            rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
-            gemm(m, m->hn, W, L.w_up, L.d.ff, W, m->act_a, L.d.ff, R, 1.0f, EPI_RELU2);
-            gemm(m, m->act_a, L.d.ff, L.w_down, W, L.d.ff, m->x, W, R, 1.0f, EPI_ADD);
-        }
-        if (m->taps_on) LCU(cudaMemcpyAsync(m->taps + run * (size_t)lens[0] * W, m->x, (size_t)lens[0] * W * 4, cudaMemcpyDeviceToDevice, m->stream));
+    } else {
+        enqueue_step(m, sm, R, n_runs, n_want, head, taps_len);
     }
-    if (n_want > 0 && (logits_out || pick_out)) {
-        rmsnorm(m, m->x, nullptr, (const float*)find(m, "final.norm")->d, m->hw, sm.want, n_want);
-        gemm(m, m->hw, W, find(m, "head")->d, p.vocab, W, m->logits, p.vocab, n_want, p.logit_scale, EPI_STORE);
-        if (pick_out) {
-            launch(m, lp_argmax_kernel, dim3(n_want), dim3(1024), 0, (const float*)m->logits, p.vocab, m->pick);
-            LCU(cudaMemcpyAsync(pick_out, m->pick, (size_t)n_want * 4, cudaMemcpyDeviceToHost, m->stream));
-        } else {
-            const size_t bytes = (size_t)n_want * p.vocab * 4;
-            if (bytes > m->h_logits_bytes) {
-                if (m->h_logits) cudaFreeHost(m->h_logits);
-                m->h_logits = nullptr;
-                m->h_logits_bytes = 0;
-                LCU_ALLOC(cudaHostAlloc((void**)&m->h_logits, bytes, cudaHostAllocDefault));
-                m->h_logits_bytes = bytes;
-            }
-            LCU(cudaMemcpyAsync(m->h_logits, m->logits, bytes, cudaMemcpyDeviceToHost, m->stream));
+    if (head == 2) {
+        LCU(cudaMemcpyAsync(pick_out, m->pick, (size_t)n_want * 4, cudaMemcpyDeviceToHost, m->stream));
+    } else if (head == 1) {
+        const size_t bytes = (size_t)n_want * p.vocab * 4;
+        if (bytes > m->h_logits_bytes) {
+            if (m->h_logits) cudaFreeHost(m->h_logits);
+            m->h_logits = nullptr;
+            m->h_logits_bytes = 0;
+            LCU_ALLOC(cudaHostAlloc((void**)&m->h_logits, bytes, cudaHostAllocDefault));
+            m->h_logits_bytes = bytes;
         }
+        LCU(cudaMemcpyAsync(m->h_logits, m->logits, bytes, cudaMemcpyDeviceToHost, m->stream));
     }
+    LCU(cudaMemcpyAsync(m->h_tc_err, m->tc_err, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
     LCU(cudaStreamSynchronize(m->stream));
     LCU(cudaGetLastError());
+    if (*m->h_tc_err) {   // a bounded wait of the tensor-core GEMM gave up: the step's results are void
+        const int code = *m->h_tc_err;
+        *m->h_tc_err = 0;
+        cudaMemset(m->tc_err, 0, sizeof(int));
+        return lp_fail(err, B200_ERR_OPERATION_FAILED, "b200_step: tensor-core GEMM wait gave up (code " + std::to_string(code) + "): results discarded");
+    }
     if (n_want > 0 && logits_out) memcpy(logits_out, m->h_logits, (size_t)n_want * p.vocab * 4);
     return B200_OK;
 }

@@ -57,6 +57,37 @@ def parse_config(cfg, max_seq_len, max_batch, compute="bfloat16"):
     return program, layers
 
 
+def tensor_shapes(cfg):
+    """name -> shape of every tensor a model of this config holds (what model.safetensors must contain)."""
+    W, V = cfg["width"], cfg["vocab"]
+    out = {"embed": (V, W), "head": (V, W), "final.norm": (W,)}
+    lp = cfg["loop"]
+    if lp["stop"] > lp["start"]:
+        out["loop.step"] = (lp["times"], W)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = "l%d." % i, L["mixer"]
+        out[p + "norm1"] = (W,)
+        if L["type"] == "parallel":
+            le, ri = m["left"], m["right"]
+            q = p + "mix.left."
+            out.update({q + "q": (le["heads"] * le["dim"], W), q + "k": (le["kv_heads"] * le["dim"], W), q + "v": (le["kv_heads"] * le["vdim"], W),
+                        q + "q.norm": (le["dim"],), q + "k.norm": (le["dim"],), q + "g": (le["heads"] * le["vdim"], W),
+                        q + "o": (W, le["heads"] * le["vdim"])})
+            r = p + "mix.right."
+            out.update({r + "q": (ri["heads"] * ri["dim"], W), r + "k": (ri["heads"] * ri["dim"], W), r + "v": (ri["heads"] * ri["vdim"], W),
+                        r + "g": (ri["heads"] * ri["vdim"], W), r + "o": (W, ri["heads"] * ri["vdim"]), r + "norm": (ri["heads"] * ri["vdim"],),
+                        r + "i": (ri["heads"], W), r + "i.b": (ri["heads"],), r + "f": (ri["heads"], W), r + "f.b": (ri["heads"],)})
+        else:
+            x = p + "mix."
+            qk, vv = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"]
+            out.update({x + "q": (qk, W), x + "q.conv": (qk, m["conv"]), x + "k": (qk, W), x + "k.conv": (qk, m["conv"]),
+                        x + "v": (vv, W), x + "v.conv": (vv, m["conv"]), x + "b": (m["heads"], W), x + "A_log": (m["heads"],),
+                        x + "norm": (m["vdim"],), x + "a": (m["heads"], W), x + "dt_bias": (m["heads"],), x + "g": (vv, W), x + "o": (W, vv)})
+        if L["mlp"]:
+            out.update({p + "norm2": (W,), p + "mlp.up": (L["mlp"]["ff"], W), p + "mlp.down": (W, L["mlp"]["ff"])})
+    return out
+
+
 def load(model_dir, max_seq_len=4096, max_batch=8, compute="bfloat16", device=0, taps=False):
     """A folder with config.json and model.safetensors -> a finalized context."""
     with open(os.path.join(model_dir, "config.json")) as f:
@@ -64,8 +95,18 @@ def load(model_dir, max_seq_len=4096, max_batch=8, compute="bfloat16", device=0,
     program, layers = parse_config(cfg, max_seq_len, max_batch, compute)
     st = SafetensorsFile(os.path.join(model_dir, "model.safetensors"))
 
+    want = tensor_shapes(cfg)
+    missing = sorted(set(want) - set(st.names()))
+    if missing:
+        raise InvalidArgument(f"{model_dir}: model.safetensors lacks {missing[:4]}{' ...' if len(missing) > 4 else ''}")
+    for name, shape in want.items():
+        if tuple(st.shape(name)) != tuple(shape):
+            raise InvalidArgument(f"{model_dir}: tensor {name} has shape {st.shape(name)}, the config wants {tuple(shape)}")
+
     def feeder(upload):
         for name in st.names():
+            if name not in want:
+                continue
             gg, shape, arr = st.tensor(name)
             if gg is None:
                 continue                      # integer tables: this design has none the engine reads

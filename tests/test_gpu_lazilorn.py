@@ -378,3 +378,29 @@ def test_bad_arguments(b200):
     del w["l0.mix.A_log"]
     with pytest.raises(b200.InvalidArgument):
         S.gpu_model(cfg, w)
+
+
+# ---------------------------------------------------------------------------------------------------- tensor-core GEMM
+def test_tensor_core_gemm_against_cuda_core_gemm(b200, monkeypatch):
+    # bf16 mode, sizes that reach every tile width of the tcgen05 kernel (rows 40 / 100 / 300), a K that is not a multiple of 64,
+    # output widths that are not multiples of 128; the CUDA-core kernel multiplies the same bf16 values, so the two paths differ
+    # only in the order of the f32 sums (and in the bf16 roundings of later activations that such a difference flips)
+    cfg = S.config([S.parallel_layer(heads=4, kv_heads=2, dim=32, vdim=40, window=50, keep_first=3, mheads=3, mdim=32, mvdim=40, ff=200),
+                    S.delta_layer(heads=4, kv_heads=2, dim=32, vdim=48, conv=4, ff=136)], width=168, vocab=300)
+    w = S.random_weights(cfg, 43)
+    toks = tokens(300, cfg["vocab"], 44)
+    outs = {}
+    for tc in ("1", "0"):
+        monkeypatch.setenv("B200_LP_TC", tc)
+        gpu = S.gpu_model(cfg, w, "bfloat16", max_seq_len=320)
+        try:
+            rows = [gpu.step([(0, toks[:n])], list(range(n))) for n in (40, 100)]
+            gpu.reset(0)
+            gpu.reset(1)
+            rows.append(gpu.step([(1, toks)], list(range(300))))
+            outs[tc] = rows
+        finally:
+            gpu.close()
+    for a, b in zip(outs["1"], outs["0"]):
+        assert S.rel_err(a, b) < 1.5e-2
+    assert S.rel_err(outs["1"][2], O.Model(cfg, w).forward(toks)) < BF16_TOL
