@@ -541,29 +541,41 @@ struct MemGeom {
     int q_off, k_off, v_off, i_off, f_off;
     size_t rec_off;
 };
-constexpr int SCAN_BD = 64;
-// Tokens are staged into shared memory SCAN_CH at a time (coalesced loads, gates and unit norms worked out one token per thread), so
-// the serial loop over a chunk's tokens runs out of shared memory and registers: one global round trip per chunk instead of three
-// per token.
-template <int DMAX> struct ScanChunk { static constexpr int N = DMAX > 128 ? 8 : 32; };
+constexpr int SCAN_BD = 64, SCAN_DREG = 32;
+// How the scans are laid out.  A state column S[:, j] is cut into pieces of SCAN_DREG = 32 key channels, one piece per thread in
+// registers: DMAX / 32 neighbouring lanes share a column (partial dot products meet through shuffles) and a block of 64 threads covers
+// 64 / (DMAX / 32) columns, so wide keys mean more blocks and a shorter serial chain per token, not more registers.  Tokens are staged
+// SCAN_CH at a time with 4-byte cp.async copies (all in flight together: one global round trip per chunk), gates and unit norms are
+// worked out one token per thread / warp, and the serial loop over the chunk's tokens runs out of shared memory and registers.
+template <int DMAX> struct ScanChunk { static constexpr int N = DMAX > 128 ? 16 : 32; };
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+template <int SPLIT>
+__device__ __forceinline__ float split_sum(float v) {   // sum over the SPLIT neighbouring lanes that share a column
+#pragma unroll
+    for (int o = 1; o < SPLIT; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
 template <int DMAX>
 __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, MemGeom g, const float* __restrict__ P, int ldp,
                                                                    const float* __restrict__ ib, const float* __restrict__ fb,
                                                                    float* __restrict__ O, int ldo) {
-    constexpr int CH = ScanChunk<DMAX>::N;
+    constexpr int CH = ScanChunk<DMAX>::N, SPLIT = DMAX / SCAN_DREG, COLS = SCAN_BD / SPLIT;
     __shared__ __align__(16) float qs[CH][DMAX];
     __shared__ __align__(16) float ks[CH][DMAX];
-    __shared__ float vs[CH][SCAN_BD], il_s[CH], fl_s[CH];
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int j = blockIdx.x * SCAN_BD + tid, h = blockIdx.y, run = blockIdx.z;
+    __shared__ float vs[CH][COLS], il_s[CH], fl_s[CH];
+    const int tid = threadIdx.x, lane = tid & 31, col = tid / SPLIT, d0 = (tid % SPLIT) * SCAN_DREG;
+    const int j = blockIdx.x * COLS + col, h = blockIdx.y, run = blockIdx.z;
     const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
     float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
     float* ng = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim + (size_t)h * g.dim;
     float* mg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim + (size_t)g.H * g.dim + h;
     const bool live = j < g.vdim;
-    float s[DMAX];
+    float s[SCAN_DREG];
 #pragma unroll
-    for (int d = 0; d < DMAX; d++) s[d] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
+    for (int i = 0; i < SCAN_DREG; i++) s[i] = (live && d0 + i < g.dim) ? Sg[(size_t)(d0 + i) * g.vdim + j] : 0.0f;
     float nreg[DMAX / 32];   // n, element lane + 32 i (every warp keeps its own copy)
 #pragma unroll
     for (int i = 0; i < DMAX / 32; i++) nreg[i] = lane + 32 * i < g.dim ? ng[lane + 32 * i] : 0.0f;
@@ -574,44 +586,47 @@ __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, 
     float m = *mg;
     const float qscale = 1.0f / sqrtf((float)g.dim);
     const float bi = ib[h], bf_ = fb[h];
+    const int jc = blockIdx.x * COLS + (tid % COLS);   // the column this thread stages
     for (int c0 = r0; c0 < r1; c0 += CH) {
         const int nt = min(CH, r1 - c0);
         __syncthreads();   // the previous chunk has been consumed
-        for (int i = tid; i < nt * g.dim; i += SCAN_BD) {
-            const int t = i / g.dim, d = i - t * g.dim;
+        for (int t = 0; t < nt; t++) {
             const float* p = P + (size_t)(c0 + t) * ldp;
-            qs[t][d] = p[g.q_off + h * g.dim + d] * qscale;
-            ks[t][d] = p[g.k_off + h * g.dim + d];
+            for (int d = tid; d < g.dim; d += SCAN_BD) {
+                cp_async4(&qs[t][d], p + g.q_off + h * g.dim + d);
+                cp_async4(&ks[t][d], p + g.k_off + h * g.dim + d);
+            }
         }
-        for (int i = tid; i < nt * SCAN_BD; i += SCAN_BD) {
-            const int t = i / SCAN_BD;
-            vs[t][tid] = live ? P[(size_t)(c0 + t) * ldp + g.v_off + h * g.vdim + j] : 0.0f;
+        for (int t = tid / COLS; t < nt; t += SPLIT) {
+            if (jc < g.vdim) cp_async4(&vs[t][tid % COLS], P + (size_t)(c0 + t) * ldp + g.v_off + h * g.vdim + jc);
+            else vs[t][tid % COLS] = 0.0f;
         }
         if (tid < nt) {
             const float* p = P + (size_t)(c0 + tid) * ldp;
             il_s[tid] = g.cap * tanhf((p[g.i_off + h] + bi) / g.cap);
             fl_s[tid] = logsigmoid_f(g.cap * tanhf((p[g.f_off + h] + bf_) / g.cap));
         }
+        cp_async_wait_all();
         __syncthreads();
         for (int t = 0; t < nt; t++) {
             const float il = il_s[t], fl = fl_s[t];
             const float m_new = fmaxf(fl + m, il);
             const float fa = expf(fl + m - m_new), ia = expf(il - m_new);
             m = m_new;
-            const float iv = ia * vs[t][tid];
+            const float iv = ia * vs[t][col];
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-            for (int d = 0; d < DMAX; d += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][d]);
-                s[d] = fmaf(fa, s[d], k4.x * iv);
-                s[d + 1] = fmaf(fa, s[d + 1], k4.y * iv);
-                s[d + 2] = fmaf(fa, s[d + 2], k4.z * iv);
-                s[d + 3] = fmaf(fa, s[d + 3], k4.w * iv);
-                a0 = fmaf(s[d], q4.x, a0);
-                a1 = fmaf(s[d + 1], q4.y, a1);
-                a2 = fmaf(s[d + 2], q4.z, a2);
-                a3 = fmaf(s[d + 3], q4.w, a3);
+            for (int i = 0; i < SCAN_DREG; i += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d0 + i]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][d0 + i]);
+                s[i] = fmaf(fa, s[i], k4.x * iv);
+                s[i + 1] = fmaf(fa, s[i + 1], k4.y * iv);
+                s[i + 2] = fmaf(fa, s[i + 2], k4.z * iv);
+                s[i + 3] = fmaf(fa, s[i + 3], k4.w * iv);
+                a0 = fmaf(s[i], q4.x, a0);
+                a1 = fmaf(s[i + 1], q4.y, a1);
+                a2 = fmaf(s[i + 2], q4.z, a2);
+                a3 = fmaf(s[i + 3], q4.w, a3);
             }
             float nq = 0.0f;
 #pragma unroll
@@ -619,14 +634,15 @@ __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, 
                 nreg[i] = fmaf(fa, nreg[i], ia * ks[t][lane + 32 * i]);
                 nq = fmaf(nreg[i], qs[t][lane + 32 * i], nq);
             }
-            nq = wsum(nq);
-            if (live) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = ((a0 + a1) + (a2 + a3)) / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+            nq = wsum(nq) * qscale;
+            const float acc = split_sum<SPLIT>((a0 + a1) + (a2 + a3)) * qscale;
+            if (live && d0 == 0) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = acc / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
         }
     }
     if (live)
 #pragma unroll
-        for (int d = 0; d < DMAX; d++)
-            if (d < g.dim) Sg[(size_t)d * g.vdim + j] = s[d];
+        for (int i = 0; i < SCAN_DREG; i++)
+            if (d0 + i < g.dim) Sg[(size_t)(d0 + i) * g.vdim + j] = s[i];
     if (blockIdx.x == 0 && tid < 32) {
 #pragma unroll
         for (int i = 0; i < DMAX / 32; i++)
@@ -670,27 +686,27 @@ __global__ void lp_conv_tail_kernel(StepMeta sm, DeltaGeom g, const float* __res
             tail[(size_t)i * g.C + c] = st >= 0 ? P[(size_t)(r0 + st) * ldp + c] : tail[(size_t)(i + len) * g.C + c];
         }
 }
-// Per (run, head): thread = value channel j with S[:, j] in registers.  q, k become unit vectors (x / sqrt(sum x^2 + 1e-6), q also
-// times dim^(-1/2)); beta = sigmoid(zb); decay = exp(-exp(A_log) softplus(za + dt_bias));
+// Per (run, head), laid out like the matrix-memory scan.  q, k become unit vectors (x / sqrt(sum x^2 + 1e-6), q also times
+// dim^(-1/2)): a warp normalises one staged vector at a time in shared memory; beta = sigmoid(zb);
+// decay = exp(-exp(A_log) softplus(za + dt_bias));
 //   S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q   (the read-out sees this token's write).
-// Chunks of tokens are staged as in the matrix-memory kernel: a warp normalises q and k of one token at a time.
 template <int DMAX>
 __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, DeltaGeom g, const float* __restrict__ QKV, const float* __restrict__ P,
                                                                  int ldp, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                                                                  float* __restrict__ O, int ldo) {
-    constexpr int CH = ScanChunk<DMAX>::N;
+    constexpr int CH = ScanChunk<DMAX>::N, SPLIT = DMAX / SCAN_DREG, COLS = SCAN_BD / SPLIT;
     __shared__ __align__(16) float qs[CH][DMAX];
     __shared__ __align__(16) float ks[CH][DMAX];
-    __shared__ float vs[CH][SCAN_BD], beta_s[CH], dec_s[CH];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int j = blockIdx.x * SCAN_BD + tid, h = blockIdx.y, run = blockIdx.z;
+    __shared__ float vs[CH][COLS], beta_s[CH], dec_s[CH];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, col = tid / SPLIT, d0 = (tid % SPLIT) * SCAN_DREG;
+    const int j = blockIdx.x * COLS + col, h = blockIdx.y, run = blockIdx.z;
     const int hk = h / (g.H / g.G);
     const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
     float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
     const bool live = j < g.vdim;
-    float s[DMAX];
+    float s[SCAN_DREG];
 #pragma unroll
-    for (int d = 0; d < DMAX; d++) s[d] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
+    for (int i = 0; i < SCAN_DREG; i++) s[i] = (live && d0 + i < g.dim) ? Sg[(size_t)(d0 + i) * g.vdim + j] : 0.0f;
     for (int i = tid; i < CH * DMAX; i += SCAN_BD) {
         (&qs[0][0])[i] = 0.0f;
         (&ks[0][0])[i] = 0.0f;
@@ -698,66 +714,75 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
     const float rate = expf(A_log[h]), dtb = dt_bias[h];
     const float qscale = 1.0f / sqrtf((float)g.dim);
     const int k_col = g.G * g.dim, v_col = 2 * g.G * g.dim;
+    const int jc = blockIdx.x * COLS + (tid % COLS);
     for (int c0 = r0; c0 < r1; c0 += CH) {
         const int nt = min(CH, r1 - c0);
         __syncthreads();
-        for (int t = warp; t < 2 * nt; t += SCAN_BD / 32) {   // (token, q or k) pairs, one per warp at a time
-            const int tt = t >> 1, isk = t & 1;
-            const float* src = QKV + (size_t)(c0 + tt) * g.C + (isk ? k_col : 0) + hk * g.dim;
-            float ss = 0.0f;
-            for (int d = lane; d < g.dim; d += 32) ss += src[d] * src[d];
-            ss = wsum(ss);
-            const float inv = (isk ? 1.0f : qscale) / sqrtf(ss + 1e-6f);
-            float* dst = isk ? ks[tt] : qs[tt];
-            for (int d = lane; d < g.dim; d += 32) dst[d] = src[d] * inv;
+        for (int t = 0; t < nt; t++) {
+            const float* x = QKV + (size_t)(c0 + t) * g.C + hk * g.dim;
+            for (int d = tid; d < g.dim; d += SCAN_BD) {
+                cp_async4(&qs[t][d], x + d);
+                cp_async4(&ks[t][d], x + k_col + d);
+            }
         }
-        for (int i = tid; i < nt * SCAN_BD; i += SCAN_BD) {
-            const int t = i / SCAN_BD;
-            vs[t][tid] = live ? QKV[(size_t)(c0 + t) * g.C + v_col + h * g.vdim + j] : 0.0f;
+        for (int t = tid / COLS; t < nt; t += SPLIT) {
+            if (jc < g.vdim) cp_async4(&vs[t][tid % COLS], QKV + (size_t)(c0 + t) * g.C + v_col + h * g.vdim + jc);
+            else vs[t][tid % COLS] = 0.0f;
         }
         if (tid < nt) {
             const float* p = P + (size_t)(c0 + tid) * ldp;
             beta_s[tid] = sigmoid_f(p[g.b_off + h]);
             dec_s[tid] = expf(-rate * softplus_f(p[g.a_off + h] + dtb));
         }
+        cp_async_wait_all();
+        __syncthreads();
+        for (int t = warp; t < 2 * nt; t += SCAN_BD / 32) {   // (token, q or k) pairs, one per warp at a time
+            float* vec = (t & 1) ? ks[t >> 1] : qs[t >> 1];
+            float ss = 0.0f;
+            for (int d = lane; d < g.dim; d += 32) ss += vec[d] * vec[d];
+            ss = wsum(ss);
+            const float inv = ((t & 1) ? 1.0f : qscale) / sqrtf(ss + 1e-6f);
+            for (int d = lane; d < g.dim; d += 32) vec[d] *= inv;
+        }
         __syncthreads();
         for (int t = 0; t < nt; t++) {
-            const float decay = dec_s[t], beta = beta_s[t], v = vs[t][tid];
+            const float decay = dec_s[t], beta = beta_s[t], v = vs[t][col];
             float k0 = 0.0f, k1 = 0.0f, k2 = 0.0f, k3 = 0.0f;
 #pragma unroll
-            for (int d = 0; d < DMAX; d += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d]);
-                s[d] *= decay;
-                s[d + 1] *= decay;
-                s[d + 2] *= decay;
-                s[d + 3] *= decay;
-                k0 = fmaf(s[d], k4.x, k0);
-                k1 = fmaf(s[d + 1], k4.y, k1);
-                k2 = fmaf(s[d + 2], k4.z, k2);
-                k3 = fmaf(s[d + 3], k4.w, k3);
+            for (int i = 0; i < SCAN_DREG; i += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d0 + i]);
+                s[i] *= decay;
+                s[i + 1] *= decay;
+                s[i + 2] *= decay;
+                s[i + 3] *= decay;
+                k0 = fmaf(s[i], k4.x, k0);
+                k1 = fmaf(s[i + 1], k4.y, k1);
+                k2 = fmaf(s[i + 2], k4.z, k2);
+                k3 = fmaf(s[i + 3], k4.w, k3);
             }
-            const float u = beta * (v - ((k0 + k1) + (k2 + k3)));
+            const float u = beta * (v - split_sum<SPLIT>((k0 + k1) + (k2 + k3)));
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-            for (int d = 0; d < DMAX; d += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][d]);
-                s[d] = fmaf(k4.x, u, s[d]);
-                s[d + 1] = fmaf(k4.y, u, s[d + 1]);
-                s[d + 2] = fmaf(k4.z, u, s[d + 2]);
-                s[d + 3] = fmaf(k4.w, u, s[d + 3]);
-                a0 = fmaf(s[d], q4.x, a0);
-                a1 = fmaf(s[d + 1], q4.y, a1);
-                a2 = fmaf(s[d + 2], q4.z, a2);
-                a3 = fmaf(s[d + 3], q4.w, a3);
+            for (int i = 0; i < SCAN_DREG; i += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d0 + i]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][d0 + i]);
+                s[i] = fmaf(k4.x, u, s[i]);
+                s[i + 1] = fmaf(k4.y, u, s[i + 1]);
+                s[i + 2] = fmaf(k4.z, u, s[i + 2]);
+                s[i + 3] = fmaf(k4.w, u, s[i + 3]);
+                a0 = fmaf(s[i], q4.x, a0);
+                a1 = fmaf(s[i + 1], q4.y, a1);
+                a2 = fmaf(s[i + 2], q4.z, a2);
+                a3 = fmaf(s[i + 3], q4.w, a3);
             }
-            if (live) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = (a0 + a1) + (a2 + a3);
+            const float acc = split_sum<SPLIT>((a0 + a1) + (a2 + a3));
+            if (live && d0 == 0) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = acc;
         }
     }
     if (live)
 #pragma unroll
-        for (int d = 0; d < DMAX; d++)
-            if (d < g.dim) Sg[(size_t)d * g.vdim + j] = s[d];
+        for (int i = 0; i < SCAN_DREG; i++)
+            if (d0 + i < g.dim) Sg[(size_t)(d0 + i) * g.vdim + j] = s[i];
 }
 
 // out[r][h][c] = o / sqrt(mean_c o^2 + eps) * w[w_per_head ? c : h * vdim + c] * act(gate), act = sigmoid (0) or SiLU (1); one warp
@@ -1431,7 +1456,8 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             MemGeom mg = L.mg;
             mg.rec_off = m->run_rec_off[run];
             const int ldo = mg.H * mg.vdim;
-            dim3 sgrid((mg.vdim + SCAN_BD - 1) / SCAN_BD, mg.H, n_runs);
+            const int mcols = SCAN_BD / (pick_dmax(mg.dim) / SCAN_DREG);
+            dim3 sgrid((mg.vdim + mcols - 1) / mcols, mg.H, n_runs);
             switch (pick_dmax(mg.dim)) {
                 case 32: launch(m, lp_matrix_memory_kernel<32>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
                 case 64: launch(m, lp_matrix_memory_kernel<64>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
@@ -1449,7 +1475,8 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, m->conv);
             if (dg.taps > 1) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
             const int ldo = dg.H * dg.vdim;
-            dim3 sgrid((dg.vdim + SCAN_BD - 1) / SCAN_BD, dg.H, n_runs);
+            const int dcols = SCAN_BD / (pick_dmax(dg.dim) / SCAN_DREG);
+            dim3 sgrid((dg.vdim + dcols - 1) / dcols, dg.H, n_runs);
             switch (pick_dmax(dg.dim)) {
                 case 32: launch(m, lp_gated_delta_kernel<32>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
                 case 64: launch(m, lp_gated_delta_kernel<64>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
