@@ -530,6 +530,177 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
     }
 }
 
+// Prompt rows in bf16 mode: 64 queries of one (run, head) per block, 16 per warp, against key tiles of 64 staged in shared memory as
+// bf16 (K as [key][dim], V transposed as [channel][key]); scores and the value sum run on the tensor pipe (mma.sync m16n8k16, bf16
+// operands, f32 accumulators), the mask, the online softmax and the normalisation in f32 registers.  The probabilities go from
+// the accumulator layout of the score tile straight into the A operand of the value product.  DK / DV are upper bounds of the key
+// and value sizes (multiples of 16 / 8 at run time); the visible keys of a tile of queries are [0, min(keep_first, lo0)) and
+// [lo0, last query], lo0 = the window start of its first query, every element masked by the rule itself.
+__device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+constexpr int AT_Q = 64, AT_K = 64;
+template <int DK, int DV>
+__global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, AttnGeom a, const float* __restrict__ qbuf,
+                                                                  const float* __restrict__ P, int ldp, bf16* __restrict__ out) {
+    constexpr int KS = DK + 8, VS = AT_K + 8;          // row pitches in bf16: conflict-free 32-bit fragment loads
+    extern __shared__ __align__(16) uint8_t at_smem[];
+    bf16* Ks = reinterpret_cast<bf16*>(at_smem);        // [AT_K][KS]
+    bf16* Vt = Ks + AT_K * KS;                          // [DV][VS]
+    const int run = blockIdx.z, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const int r0 = sm.run_start[run], len = sm.run_start[run + 1] - r0, p0 = sm.run_pos0[run];
+    const int t0 = blockIdx.x * AT_Q;
+    if (t0 >= len) return;
+    const int g = h / (a.H / a.G);
+    const float* kc = reinterpret_cast<const float*>(sm.run_kv[run] + a.kv_off);
+    const float* vc = kc + (size_t)a.cap * a.G * a.dim;
+    const int ldk = a.G * a.dim, ldv = a.G * a.vdim;
+    // this thread's two query rows (gid and gid + 8 of the warp's 16) and their positions
+    const int tq0 = t0 + warp * 16 + gid, tq1 = tq0 + 8;
+    const int i0 = p0 + tq0, i1 = p0 + tq1;
+    const bool ok0 = tq0 < len, ok1 = tq1 < len;
+    uint32_t qa[DK / 16][4];
+#pragma unroll
+    for (int kb = 0; kb < DK / 16; kb++) {
+        const int d = kb * 16 + 2 * tig;
+        const float* q0 = qbuf + (size_t)(r0 + tq0) * a.H * a.dim + h * a.dim;
+        const float* q1 = qbuf + (size_t)(r0 + tq1) * a.H * a.dim + h * a.dim;
+        const bool in = d < a.dim;       // dim is a multiple of 16: d + 9 < dim too
+        qa[kb][0] = (ok0 && in) ? pack_bf2(q0[d], q0[d + 1]) : 0u;
+        qa[kb][1] = (ok1 && in) ? pack_bf2(q1[d], q1[d + 1]) : 0u;
+        qa[kb][2] = (ok0 && in) ? pack_bf2(q0[d + 8], q0[d + 9]) : 0u;
+        qa[kb][3] = (ok1 && in) ? pack_bf2(q1[d + 8], q1[d + 9]) : 0u;
+    }
+    float o[DV / 8][4];
+#pragma unroll
+    for (int n = 0; n < DV / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    const int first = p0 + t0, last = p0 + min(t0 + AT_Q, len) - 1;
+    const int lo0 = max(0, first - a.window + 1);
+    const int a_end = min(a.keep_first, lo0);
+    for (int part = 0; part < 2; part++) {
+        const int beg = part ? lo0 : 0, end = part ? last + 1 : a_end;
+        for (int j0 = beg; j0 < end; j0 += AT_K) {
+            const int nk = min(AT_K, end - j0);
+            __syncthreads();   // the previous tile has been consumed
+            for (int i = threadIdx.x; i < AT_K * (DK / 4); i += 128) {
+                const int key = i / (DK / 4), d = (i - key * (DK / 4)) * 4;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (key < nk && d < a.dim) v = *reinterpret_cast<const float4*>(kc + (size_t)(j0 + key) * ldk + g * a.dim + d);
+                uint2 w;
+                w.x = pack_bf2(v.x, v.y);
+                w.y = pack_bf2(v.z, v.w);
+                *reinterpret_cast<uint2*>(Ks + key * KS + d) = w;
+            }
+            for (int i = threadIdx.x; i < AT_K * (DV / 4); i += 128) {
+                const int key = i / (DV / 4), c = (i - key * (DV / 4)) * 4;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (key < nk && c < a.vdim) v = *reinterpret_cast<const float4*>(vc + (size_t)(j0 + key) * ldv + g * a.vdim + c);
+                Vt[(c + 0) * VS + key] = __float2bfloat16_rn(v.x);
+                Vt[(c + 1) * VS + key] = __float2bfloat16_rn(v.y);
+                Vt[(c + 2) * VS + key] = __float2bfloat16_rn(v.z);
+                Vt[(c + 3) * VS + key] = __float2bfloat16_rn(v.w);
+            }
+            __syncthreads();
+            // scores of 16 queries x 64 keys
+            float sc[AT_K / 8][4];
+#pragma unroll
+            for (int n = 0; n < AT_K / 8; n++) {
+                sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+                const bf16* kr = Ks + (n * 8 + gid) * KS + 2 * tig;
+#pragma unroll
+                for (int kb = 0; kb < DK / 16; kb++) {
+                    if (kb * 16 < a.dim) {
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + kb * 16);
+                        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + kb * 16 + 8);
+                        mma_bf16(sc[n], qa[kb], b0, b1);
+                    }
+                }
+            }
+            // mask, scale, running maximum per row
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < AT_K / 8; n++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int key = n * 8 + 2 * tig + (e & 1), j = j0 + key;
+                    const int i = (e & 2) ? i1 : i0;
+                    const bool vis = key < nk && ((e & 2) ? ok1 : ok0) && j <= i && (i - j < a.window || j < a.keep_first);
+                    sc[n][e] = vis ? sc[n][e] * a.scale : -INFINITY;
+                }
+                mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
+                mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+            const float c0 = n0 == -INFINITY ? 1.0f : expf(m0 - n0), c1 = n1 == -INFINITY ? 1.0f : expf(m1 - n1);
+            m0 = n0;
+            m1 = n1;
+            float s0 = 0.0f, s1 = 0.0f;
+            uint32_t pa[AT_K / 16][4];
+#pragma unroll
+            for (int n = 0; n < AT_K / 8; n++) {
+                const float e0 = n0 == -INFINITY ? 0.0f : expf(sc[n][0] - n0), e1 = n0 == -INFINITY ? 0.0f : expf(sc[n][1] - n0);
+                const float e2 = n1 == -INFINITY ? 0.0f : expf(sc[n][2] - n1), e3 = n1 == -INFINITY ? 0.0f : expf(sc[n][3] - n1);
+                s0 += e0 + e1;
+                s1 += e2 + e3;
+                pa[n >> 1][(n & 1) * 2] = pack_bf2(e0, e1);
+                pa[n >> 1][(n & 1) * 2 + 1] = pack_bf2(e2, e3);
+            }
+            s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+            s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+            l0 = l0 * c0 + s0;
+            l1 = l1 * c1 + s1;
+#pragma unroll
+            for (int n = 0; n < DV / 8; n++) {
+                if (n * 8 < a.vdim) {
+                    o[n][0] *= c0;
+                    o[n][1] *= c0;
+                    o[n][2] *= c1;
+                    o[n][3] *= c1;
+                    const bf16* vr = Vt + (n * 8 + gid) * VS + 2 * tig;
+#pragma unroll
+                    for (int kb = 0; kb < AT_K / 16; kb++) {
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vr + kb * 16);
+                        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(vr + kb * 16 + 8);
+                        mma_bf16(o[n], pa[kb], b0, b1);
+                    }
+                }
+            }
+        }
+    }
+    const float inv0 = ok0 ? 1.0f / l0 : 0.0f, inv1 = ok1 ? 1.0f / l1 : 0.0f;
+    const float* gate0 = P + (size_t)(r0 + tq0) * ldp + a.g_off + h * a.vdim;
+    const float* gate1 = P + (size_t)(r0 + tq1) * ldp + a.g_off + h * a.vdim;
+    bf16* out0 = out + (size_t)(r0 + tq0) * a.H * a.vdim + h * a.vdim;
+    bf16* out1 = out + (size_t)(r0 + tq1) * a.H * a.vdim + h * a.vdim;
+#pragma unroll
+    for (int n = 0; n < DV / 8; n++) {
+        const int ch = n * 8 + 2 * tig;
+        if (ch < a.vdim) {
+            if (ok0) {
+                const float g0 = a.out_gate ? sigmoid_f(gate0[ch]) : 1.0f, g1 = a.out_gate ? sigmoid_f(gate0[ch + 1]) : 1.0f;
+                *reinterpret_cast<uint32_t*>(out0 + ch) = pack_bf2(o[n][0] * inv0 * g0, o[n][1] * inv0 * g1);
+            }
+            if (ok1) {
+                const float g0 = a.out_gate ? sigmoid_f(gate1[ch]) : 1.0f, g1 = a.out_gate ? sigmoid_f(gate1[ch + 1]) : 1.0f;
+                *reinterpret_cast<uint32_t*>(out1 + ch) = pack_bf2(o[n][2] * inv1 * g0, o[n][3] * inv1 * g1);
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ matrix memory
 // Per (run, head): S [dim][vdim], n [dim], m; thread = value channel j, its column S[:, j] lives in registers for the whole run.
 //   i = cap tanh((zi + bi) / cap),  f = logsigmoid(cap tanh((zf + bf) / cap)),  m' = max(f + m, i)
@@ -892,6 +1063,7 @@ struct LpModel {
     // tensor-core GEMM: on for bf16 steps of at least tc_min_rows rows (B200_LP_TC=0 keeps the CUDA-core kernel); *tc_err is set by a
     // bounded wait that gave up
     bool use_tc = true;
+    bool use_attn_tile = true;   // B200_LP_ATTN_TILE=0: the warp kernel for prompts too
     // decode steps replay a CUDA graph per (rows, wanted rows, head); a graph is void once a scratch buffer has moved (B200_LP_GRAPH=0: eager)
     struct Graph { cudaGraphExec_t exec = nullptr; uint64_t launches = 0, epoch = 0; bool warm = false; };
     std::map<uint64_t, Graph> graphs;
@@ -1102,6 +1274,8 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
     {
         const char* e = getenv("B200_LP_TC");
         if (e && *e) m->use_tc = atoi(e) != 0;
+        e = getenv("B200_LP_ATTN_TILE");
+        if (e && *e) m->use_attn_tile = atoi(e) != 0;
         e = getenv("B200_LP_GRAPH");
         if (e && *e) m->use_graph = atoi(e) != 0;
         e = getenv("B200_LP_TC_MIN_ROWS");
@@ -1431,9 +1605,36 @@ int ensure_scratch(LpModel* m, int R, int n_runs, int n_want, std::string* err) 
     return B200_OK;
 }
 
+// Tensor-pipe attention for prompt rows: bf16 mode, runs of at least 16 rows, key size a multiple of 16 up to 128, value size a
+// multiple of 8 up to 256 (with 16-byte aligned cache rows); everything else takes the warp kernel.
+template <int DK, int DV>
+bool attn_tile_launch(LpModel* m, const StepMeta& sm, const AttnGeom& ag, int ldp, int n_runs, int max_len) {
+    const size_t smem = (size_t)(AT_K * (DK + 8) + DV * (AT_K + 8)) * 2;
+    static bool once[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !once[dev]) {
+        if (cudaFuncSetAttribute(lp_window_attn_tile_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        if (dev >= 0 && dev < 64) once[dev] = true;
+    }
+    launch(m, lp_window_attn_tile_kernel<DK, DV>, dim3((max_len + AT_Q - 1) / AT_Q, ag.H, n_runs), dim3(128), smem, sm, ag, (const float*)m->qbuf,
+           (const float*)m->P, ldp, (bf16*)m->act_a);
+    return true;
+}
+bool attn_tile(LpModel* m, const StepMeta& sm, const AttnGeom& ag, int ldp, int n_runs, int max_len) {
+    if (m->f32 || !m->use_attn_tile || max_len < 16) return false;
+    if (ag.dim % 16 || ag.vdim % 8 || ag.dim > 128 || ag.vdim > 256 || (ag.H * ag.vdim) % 2) return false;
+    if (ag.dim <= 64 && ag.vdim <= 64) return attn_tile_launch<64, 64>(m, sm, ag, ldp, n_runs, max_len);
+    if (ag.vdim <= 128) return attn_tile_launch<128, 128>(m, sm, ag, ldp, n_runs, max_len);
+    return attn_tile_launch<128, 256>(m, sm, ag, ldp, n_runs, max_len);
+}
+
 // Every kernel of one step, in order, on the model's stream: eagerly, or while the stream is being captured into a CUDA graph (a
 // decode step: one row per run, nothing allocated).  head: 0 = no logits, 1 = logits of the wanted rows, 2 = their greedy picks.
-void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want, int head, int taps_len) {
+void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want, int head, int taps_len, int max_len) {
     const b200_program_desc& p = m->p;
     const int W = p.width;
     const float* loop_step = p.loop_stop > p.loop_start ? (const float*)find(m, "loop.step")->d : nullptr;
@@ -1449,10 +1650,13 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             AttnGeom ag = L.ag;
             ag.kv_off = m->run_kv_off[run];
             launch(m, lp_attn_prep_kernel, dim3(R), dim3(128), 0, sm, ag, (const float*)m->P, L.n_in, L.qn, L.kn, m->qbuf);
+            if (attn_tile(m, sm, ag, L.n_in, n_runs, max_len)) {
+            } else {
             dim3 agrid(R, ag.H);
             const size_t asmem = (size_t)(((ag.dim + 3) & ~3) + ATT_WARPS * ag.vdim + 2 * ATT_WARPS) * 4;
             if (m->f32) launch(m, lp_window_attn_kernel<float>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (float*)m->act_a);
             else launch(m, lp_window_attn_kernel<bf16>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (bf16*)m->act_a);
+            }
             MemGeom mg = L.mg;
             mg.rec_off = m->run_rec_off[run];
             const int ldo = mg.H * mg.vdim;
@@ -1596,6 +1800,8 @@ int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int*
         }
         m->taps_len = lens[0];
     }
+    int max_len = 1;
+    for (int i = 0; i < n_runs; i++) max_len = std::max(max_len, lens[i]);
     const int head = (n_want > 0 && pick_out) ? 2 : (n_want > 0 && logits_out) ? 1 : 0;
     const int taps_len = m->taps_on ? lens[0] : 0;
     // A decode step (one row per run, every slot already holds state) always launches the same kernels with the same arguments: the
@@ -1615,12 +1821,12 @@ int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int*
             m->launches += g.launches;
         } else if (!g.warm) {
             g.warm = true;
-            enqueue_step(m, sm, R, n_runs, n_want, head, 0);
+            enqueue_step(m, sm, R, n_runs, n_want, head, 0, 1);
         } else {
             const uint64_t before = m->launches;
             cudaGraph_t graph = nullptr;
             LCU(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
-            enqueue_step(m, sm, R, n_runs, n_want, head, 0);
+            enqueue_step(m, sm, R, n_runs, n_want, head, 0, 1);
             cudaError_t e = cudaStreamEndCapture(m->stream, &graph);
             if (e == cudaSuccess) e = cudaGraphInstantiate(&g.exec, graph, 0);
             if (graph) cudaGraphDestroy(graph);
@@ -1629,7 +1835,7 @@ int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int*
                 g = LpModel::Graph();
                 m->use_graph = false;          // fall back to eager launches for good
                 m->launches = before;
-                enqueue_step(m, sm, R, n_runs, n_want, head, 0);
+                enqueue_step(m, sm, R, n_runs, n_want, head, 0, 1);
             } else {
                 g.launches = m->launches - before;
                 g.epoch = m->scratch_epoch;
@@ -1637,7 +1843,7 @@ int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int*
             }
         }
     } else {
-        enqueue_step(m, sm, R, n_runs, n_want, head, taps_len);
+        enqueue_step(m, sm, R, n_runs, n_want, head, taps_len, max_len);
     }
     if (head == 2) {
         LCU(cudaMemcpyAsync(pick_out, m->pick, (size_t)n_want * 4, cudaMemcpyDeviceToHost, m->stream));

@@ -404,3 +404,31 @@ def test_tensor_core_gemm_against_cuda_core_gemm(b200, monkeypatch):
     for a, b in zip(outs["1"], outs["0"]):
         assert S.rel_err(a, b) < 1.5e-2
     assert S.rel_err(outs["1"][2], O.Model(cfg, w).forward(toks)) < BF16_TOL
+
+
+@pytest.mark.parametrize("dims", [(16, 24, 11, 4), (32, 40, 70, 0), (96, 136, 23, 30), (128, 128, 64, 1)])
+def test_tile_attention_against_warp_attention(b200, monkeypatch, dims):
+    # bf16 prompts take the tensor-pipe attention kernel when the head sizes allow it; the warp kernel computes the same thing in
+    # f32.  Windows that end inside, at and across key tiles of 64; kept tokens shorter and longer than the window; several unequal
+    # runs in one step, one of them continued afterwards (its cache then holds rows of both steps).
+    dim, vdim, window, keep = dims
+    cfg = S.config([S.parallel_layer(heads=4, kv_heads=2, dim=dim, vdim=vdim, window=window, keep_first=keep, left_scale=1.0,
+                                     right_scale=0.0, ff=0)], width=64, vocab=80)
+    w = S.random_weights(cfg, 47)
+    a, b, c = tokens(150, cfg["vocab"], 1), tokens(64, cfg["vocab"], 2), tokens(17, cfg["vocab"], 3)
+    more = tokens(70, cfg["vocab"], 4)
+    outs = {}
+    for tile in ("1", "0"):
+        monkeypatch.setenv("B200_LP_ATTN_TILE", tile)
+        gpu = S.gpu_model(cfg, w, "bfloat16", max_seq_len=256)
+        try:
+            first = gpu.step([(0, a), (1, b), (2, c)], list(range(len(a) + len(b) + len(c))))
+            second = gpu.step([(1, more)], list(range(len(more))))
+            outs[tile] = np.concatenate([first, second])
+        finally:
+            gpu.close()
+    ref = O.Model(cfg, w)
+    want = np.concatenate([ref.forward(a), ref.forward(b + more)[:len(b)], ref.forward(c), ref.forward(b + more)[len(b):]])
+    assert S.rel_err(outs["1"], outs["0"]) < 2e-2
+    assert S.rel_err(outs["1"], want) < BF16_TOL
+    assert S.rel_err(outs["0"], want) < BF16_TOL
