@@ -394,6 +394,65 @@ __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, i
     }
 }
 
+// The same for a normed input: the block first norms the (few) rows of the f32 residual stream into shared memory -- rms over the
+// row, times the norm weight, rounded to the compute type exactly as lp_rmsnorm_kernel does -- and then multiplies from there.
+// Every block repeats the norm (the rows are a few KB out of L2); a launch and a round trip through global memory go away.
+template <typename T, int EPI>
+__global__ void __launch_bounds__(256) lp_gemv_norm_kernel(const float* __restrict__ X, const int* __restrict__ gather, const float* __restrict__ nw,
+                                                           float eps, const T* __restrict__ W, void* __restrict__ Y, int ldy, int R, int N, int K,
+                                                           float alpha) {
+    extern __shared__ __align__(16) uint8_t gn_smem[];
+    T* xs = reinterpret_cast<T*>(gn_smem);            // [R][K]
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = 0; r < R; r++) {
+        const float* xr = X + (size_t)(gather ? gather[r] : r) * K;
+        float ss = 0.0f;
+        for (int k = threadIdx.x; k < K; k += 256) ss += xr[k] * xr[k];
+        ss = wsum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) t += red[i];
+            inv_s = 1.0f / sqrtf(t / (float)K + eps);
+        }
+        __syncthreads();
+        const float inv = inv_s;
+        for (int k = threadIdx.x; k < K; k += 256) xs[(size_t)r * K + k] = from_f<T>(xr[k] * inv * nw[k]);
+    }
+    __syncthreads();
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    constexpr int VN = Vec8<T>::N;
+    const T* wr = W + (size_t)n * K;
+    for (int rb = 0; rb < R; rb += GV_ROWS) {
+        const int nr = min(GV_ROWS, R - rb);
+        float acc[GV_ROWS] = {};
+        for (int k = lane * VN; k < K; k += 32 * VN) {   // (K is a multiple of VN: checked by the host)
+            float wv[VN], xv[VN];
+            Vec8<T>::load(wr + k, wv);
+#pragma unroll
+            for (int i = 0; i < GV_ROWS; i++) {
+                if (i < nr) {
+                    Vec8<T>::load(xs + (size_t)(rb + i) * K + k, xv);
+#pragma unroll
+                    for (int e = 0; e < VN; e++) acc[i] = fmaf(wv[e], xv[e], acc[i]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < GV_ROWS; i++) {
+            if (i < nr) {
+                const float sum = wsum(acc[i]);
+                if (lane == 0) epi_store<T, EPI>(Y, (size_t)(rb + i) * ldy + n, alpha * sum);
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ windowed attention
 // After the fused projection P[r] = [q | k | v | gate | ...]: per-head RMS norm of q and k (shared weight of size dim), q to qbuf,
 // k and v to the run's cache rows at the row's position.  Cache of a run: K [cap][G * dim] then V [cap][G * vdim], f32.
@@ -402,6 +461,9 @@ struct AttnGeom {
     float scale, eps;
     int q_off, k_off, v_off, g_off;   // columns of P
     size_t kv_off;                    // byte offset of this layer run inside a slot's cache block
+    int out_ld;                       // row pitch of the output (the two branches of a mixer share one buffer: [attention | memory])
+    float out_scale;                  // weight of the branch in the mixer's sum, applied before the rounding to the compute type
+    int fused_prep;                   // the attention kernel norms q / k and writes the row's K, V itself (decoding: no prep launch)
     int cap;                          // positions a slot's cache holds
 };
 __global__ void lp_attn_prep_kernel(StepMeta sm, AttnGeom a, const float* __restrict__ P, int ldp, const float* __restrict__ qw,
@@ -433,23 +495,49 @@ __global__ void lp_attn_prep_kernel(StepMeta sm, AttnGeom a, const float* __rest
 // warps' partial (max, sum, output) triples are merged through shared memory.  Visible keys of position i: [0, min(keep_first, lo))
 // and [lo, i], lo = max(0, i - window + 1).  The output is multiplied by sigmoid(gate) when the layer has an output gate.
 constexpr int ATT_ACC = 16;   // value channels per lane: vdim <= 512
-constexpr int ATT_WARPS = 4;
+constexpr int ATT_WARPS = 8;
+constexpr int ATT_QCH = 2;    // 16-byte query chunks per lane in the split-channel score loop: dim <= 256 (wider: one key per lane)
 template <typename OutT>
 __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta sm, AttnGeom a, const float* __restrict__ qbuf,
-                                                                        const float* __restrict__ P, int ldp, OutT* __restrict__ out) {
-    extern __shared__ float smem[];
+                                                                        const float* __restrict__ P, int ldp, const float* __restrict__ qw,
+                                                                        const float* __restrict__ kw, OutT* __restrict__ out) {
+    extern __shared__ __align__(16) float smem[];
     float* qs = smem;                                  // [dim]
     float* acc_s = smem + ((a.dim + 3) & ~3);          // [ATT_WARPS][vdim]
     float* ml_s = acc_s + ATT_WARPS * a.vdim;          // [ATT_WARPS][2]
     const int r = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int run = sm.row_run[r], i = sm.row_pos[r];
     const int g = h / (a.H / a.G);
-    const float* q = qbuf + (size_t)r * a.H * a.dim + h * a.dim;
-    for (int d = threadIdx.x; d < a.dim; d += blockDim.x) qs[d] = q[d];
-    __syncthreads();
     const float* kc = reinterpret_cast<const float*>(sm.run_kv[run] + a.kv_off);
     const float* vc = kc + (size_t)a.cap * a.G * a.dim;
     const int ldk = a.G * a.dim, ldv = a.G * a.vdim;
+    if (a.fused_prep) {
+        // what lp_attn_prep_kernel does, for this head and its K/V group only: warp 0 norms q into shared memory, warp 1 norms k
+        // into the cache row of this position, the other warps copy v there.  Every head of a group writes the same values; a
+        // block reads back its own writes after the barrier.
+        const float* p = P + (size_t)r * ldp;
+        if (warp < 2) {
+            const float* src = warp ? p + a.k_off + g * a.dim : p + a.q_off + h * a.dim;
+            float* dst = warp ? const_cast<float*>(kc) + (size_t)i * ldk + g * a.dim : qs;
+            const float* w = warp ? kw : qw;
+            float inv = 1.0f;
+            if (a.qk_norm) {
+                float ss = 0.0f;
+                for (int d = lane; d < a.dim; d += 32) ss += src[d] * src[d];
+                ss = wsum(ss);
+                inv = 1.0f / sqrtf(ss / (float)a.dim + a.eps);
+            }
+            for (int d = lane; d < a.dim; d += 32) dst[d] = a.qk_norm ? src[d] * inv * w[d] : src[d];
+        } else {
+            float* dst = const_cast<float*>(vc) + (size_t)i * ldv + g * a.vdim;
+            for (int c = threadIdx.x - 64; c < a.vdim; c += blockDim.x - 64) dst[c] = p[a.v_off + g * a.vdim + c];
+        }
+        __threadfence_block();
+    } else {
+        const float* q = qbuf + (size_t)r * a.H * a.dim + h * a.dim;
+        for (int d = threadIdx.x; d < a.dim; d += blockDim.x) qs[d] = q[d];
+    }
+    __syncthreads();
     const int lo = max(0, i - a.window + 1);
     const int a_end = min(a.keep_first, lo);
     const int nb0 = (a_end + 31) >> 5, nb1 = (i + 1 - lo + 31) >> 5;
@@ -457,28 +545,44 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
     float acc[ATT_ACC];
 #pragma unroll
     for (int c = 0; c < ATT_ACC; c++) acc[c] = 0.0f;
-    const bool v4 = (a.dim & 3) == 0;
+    const bool v4 = (a.dim & 3) == 0 && a.dim <= 128 * ATT_QCH;
+    float4 qr[ATT_QCH];
+#pragma unroll
+    for (int c = 0; c < ATT_QCH; c++) {
+        const int d = (lane + 32 * c) * 4;
+        qr[c] = (v4 && d < a.dim) ? *reinterpret_cast<const float4*>(qs + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     for (int b = warp; b < nb0 + nb1; b += ATT_WARPS) {
         const int j0 = b < nb0 ? b * 32 : lo + (b - nb0) * 32;
         const int end = b < nb0 ? a_end : i + 1;
         const int j = j0 + lane;
         float s = -INFINITY;
-        if (j < end) {
-            const float* kr = kc + (size_t)j * ldk + g * a.dim;
-            float d0 = 0.0f, d1 = 0.0f;
-            if (v4) {
-#pragma unroll 4
-                for (int d = 0; d < a.dim; d += 4) {
-                    const float4 kv = *reinterpret_cast<const float4*>(kr + d);
-                    d0 = fmaf(qs[d], kv.x, d0);
-                    d1 = fmaf(qs[d + 1], kv.y, d1);
-                    d0 = fmaf(qs[d + 2], kv.z, d0);
-                    d1 = fmaf(qs[d + 3], kv.w, d1);
+        if (v4) {
+            // lanes split the key channels (coalesced 16-byte loads of one cache row per key), a butterfly sums the partial dots
+            const int cnt = min(32, end - j0);
+#pragma unroll 8
+            for (int jj = 0; jj < cnt; jj++) {
+                const float* kr = kc + (size_t)(j0 + jj) * ldk + g * a.dim;
+                float part = 0.0f;
+#pragma unroll
+                for (int c = 0; c < ATT_QCH; c++) {
+                    const int d = (lane + 32 * c) * 4;
+                    if (d < a.dim) {
+                        const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+                        part = fmaf(qr[c].x, kv.x, part);
+                        part = fmaf(qr[c].y, kv.y, part);
+                        part = fmaf(qr[c].z, kv.z, part);
+                        part = fmaf(qr[c].w, kv.w, part);
+                    }
                 }
-            } else {
-                for (int d = 0; d < a.dim; d++) d0 = fmaf(qs[d], kr[d], d0);
+                part = wsum(part);
+                if (lane == jj) s = part * a.scale;
             }
-            s = (d0 + d1) * a.scale;
+        } else if (j < end) {
+            const float* kr = kc + (size_t)j * ldk + g * a.dim;
+            float d0 = 0.0f;
+            for (int d = 0; d < a.dim; d++) d0 = fmaf(qs[d], kr[d], d0);
+            s = d0 * a.scale;
         }
         const float m_new = fmaxf(m, wmax(s));
         const float p = j < end ? expf(s - m_new) : 0.0f;
@@ -488,7 +592,7 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
 #pragma unroll
         for (int c = 0; c < ATT_ACC; c++) acc[c] *= corr;
         const int cnt = min(32, end - j0);
-#pragma unroll 4
+#pragma unroll 8
         for (int jj = 0; jj < cnt; jj++) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const float* vr = vc + (size_t)(j0 + jj) * ldv + g * a.vdim;
@@ -526,7 +630,7 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
         for (int w = 0; w < ATT_WARPS; w++) o = fmaf(acc_s[w * a.vdim + ch], wgt[w], o);
         o *= invl;
         if (a.out_gate) o *= sigmoid_f(gate[ch]);
-        out[(size_t)r * a.H * a.vdim + h * a.vdim + ch] = from_f<OutT>(o);
+        out[(size_t)r * a.out_ld + h * a.vdim + ch] = from_f<OutT>(o * a.out_scale);
     }
 }
 
@@ -680,11 +784,11 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
             }
         }
     }
-    const float inv0 = ok0 ? 1.0f / l0 : 0.0f, inv1 = ok1 ? 1.0f / l1 : 0.0f;
+    const float inv0 = ok0 ? a.out_scale / l0 : 0.0f, inv1 = ok1 ? a.out_scale / l1 : 0.0f;
     const float* gate0 = P + (size_t)(r0 + tq0) * ldp + a.g_off + h * a.vdim;
     const float* gate1 = P + (size_t)(r0 + tq1) * ldp + a.g_off + h * a.vdim;
-    bf16* out0 = out + (size_t)(r0 + tq0) * a.H * a.vdim + h * a.vdim;
-    bf16* out1 = out + (size_t)(r0 + tq1) * a.H * a.vdim + h * a.vdim;
+    bf16* out0 = out + (size_t)(r0 + tq0) * a.out_ld + h * a.vdim;
+    bf16* out1 = out + (size_t)(r0 + tq1) * a.out_ld + h * a.vdim;
 #pragma unroll
     for (int n = 0; n < DV / 8; n++) {
         const int ch = n * 8 + 2 * tig;
@@ -833,10 +937,10 @@ struct DeltaGeom {
     float eps;
 };
 __global__ void lp_conv_silu_kernel(StepMeta sm, DeltaGeom g, const float* __restrict__ P, int ldp, const float* __restrict__ cw,
-                                    float* __restrict__ out) {
+                                    float* __restrict__ out, int shift_tail) {
     const int r = blockIdx.x, run = sm.row_run[r];
     const int t = r - sm.run_start[run];
-    const float* tail = reinterpret_cast<const float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim;
+    float* tail = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim;
     for (int c = threadIdx.x; c < g.C; c += blockDim.x) {
         float y = 0.0f;
         for (int i = 0; i < g.taps; i++) {
@@ -845,6 +949,10 @@ __global__ void lp_conv_silu_kernel(StepMeta sm, DeltaGeom g, const float* __res
             y = fmaf(cw[(size_t)c * g.taps + i], in, y);
         }
         out[(size_t)r * g.C + c] = y * sigmoid_f(y);
+        if (shift_tail) {   // every run has one row (decoding): the tail moves on by this input, channel by channel
+            for (int i = 0; i + 1 < g.taps - 1; i++) tail[(size_t)i * g.C + c] = tail[(size_t)(i + 1) * g.C + c];
+            if (g.taps > 1) tail[(size_t)(g.taps - 2) * g.C + c] = P[(size_t)r * ldp + c];
+        }
     }
 }
 // After the convolution: the run's tail becomes the last taps - 1 inputs of (old tail ++ new rows).
@@ -961,7 +1069,7 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
 template <typename OutT>
 __global__ void lp_headnorm_gate_kernel(const float* __restrict__ O, int ldo, const float* __restrict__ P, int ldp, int g_off,
                                         const float* __restrict__ w, int w_per_head, int H, int vdim, float eps, int act,
-                                        OutT* __restrict__ out, int R) {
+                                        OutT* __restrict__ out, int out_ld, float out_scale, int R) {
     const int r = blockIdx.x, lane = threadIdx.x & 31;
     const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (h >= H || r >= R) return;
@@ -974,7 +1082,7 @@ __global__ void lp_headnorm_gate_kernel(const float* __restrict__ O, int ldo, co
     for (int c = lane; c < vdim; c += 32) {
         const float z = gate[c];
         const float ga = act ? z * sigmoid_f(z) : sigmoid_f(z);
-        out[(size_t)r * H * vdim + h * vdim + c] = from_f<OutT>(o[c] * inv * w[w_per_head ? c : h * vdim + c] * ga);
+        out[(size_t)r * out_ld + h * vdim + c] = from_f<OutT>(o[c] * inv * w[w_per_head ? c : h * vdim + c] * ga * out_scale);
     }
 }
 
@@ -1019,7 +1127,8 @@ struct LayerPlan {
     DeltaGeom dg{};
     const float *norm1 = nullptr, *norm2 = nullptr, *qn = nullptr, *kn = nullptr, *mem_norm = nullptr, *ib = nullptr, *fb = nullptr;
     const float *conv_w = nullptr, *A_log = nullptr, *dt_bias = nullptr, *delta_norm = nullptr;
-    void *wo_attn = nullptr, *wo_mem = nullptr, *wo_delta = nullptr, *w_up = nullptr, *w_down = nullptr;
+    void *wo_cat = nullptr, *wo_delta = nullptr, *w_up = nullptr, *w_down = nullptr;   // wo_cat: [width][attention | memory]
+    int k_cat = 0;
     size_t kv_bytes = 0, rec_bytes = 0;   // per run, per slot (kv_bytes for `cap` positions)
 };
 
@@ -1063,6 +1172,7 @@ struct LpModel {
     // tensor-core GEMM: on for bf16 steps of at least tc_min_rows rows (B200_LP_TC=0 keeps the CUDA-core kernel); *tc_err is set by a
     // bounded wait that gave up
     bool use_tc = true;
+    bool use_fuse = true;        // B200_LP_FUSE=0: every step of a layer as a kernel of its own (norm, projection, ...)
     bool use_attn_tile = true;   // B200_LP_ATTN_TILE=0: the warp kernel for prompts too
     // decode steps replay a CUDA graph per (rows, wanted rows, head); a graph is void once a scratch buffer has moved (B200_LP_GRAPH=0: eager)
     struct Graph { cudaGraphExec_t exec = nullptr; uint64_t launches = 0, epoch = 0; bool warm = false; };
@@ -1218,6 +1328,49 @@ void rmsnorm(LpModel* m, float* x, const float* add, const float* w, void* out, 
     else launch(m, lp_rmsnorm_kernel<bf16>, dim3(rows), dim3(128), 0, x, add, w, (bf16*)out, gather, m->p.width, m->p.norm_eps);
 }
 
+// norm + projection of the step's rows: one fused kernel for a few rows (decoding) when the normed rows fit in shared memory,
+// else lp_rmsnorm_kernel into `scratch` and a GEMM from there.  add: the pass vector of a repeated layer range (unfused: it is
+// written back into the stream).
+template <typename T>
+bool gemv_norm_t(LpModel* m, const float* x, const int* gather, const float* nw, const void* W, int N, int K, void* Y, int ldy, int R, float alpha,
+                 int epi) {
+    constexpr int VN = Vec8<T>::N;
+    const size_t smem = (size_t)R * K * sizeof(T);
+    if (R > 2 * GV_ROWS || K % VN || ((uintptr_t)W & 15) || smem > 96 * 1024) return false;
+    static bool once[3][64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto prep = [&](auto kern, int e) {
+        if (dev >= 0 && dev < 64 && once[e][dev]) return true;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        if (dev >= 0 && dev < 64) once[e][dev] = true;
+        return true;
+    };
+    dim3 grid((N + 7) / 8), block(256);
+    const T* w = (const T*)W;
+    if (epi == EPI_STORE) {
+        if (!prep(lp_gemv_norm_kernel<T, EPI_STORE>, 0)) return false;
+        launch(m, lp_gemv_norm_kernel<T, EPI_STORE>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha);
+    } else if (epi == EPI_RELU2) {
+        if (!prep(lp_gemv_norm_kernel<T, EPI_RELU2>, 2)) return false;
+        launch(m, lp_gemv_norm_kernel<T, EPI_RELU2>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha);
+    } else return false;
+    return true;
+}
+void norm_gemm(LpModel* m, float* x, const float* add, const int* gather, const float* nw, void* scratch, const void* W, int N, void* Y, int ldy,
+               int R, float alpha, int epi) {
+    const int K = m->p.width;
+    if (!add && m->use_fuse) {
+        if (m->f32 ? gemv_norm_t<float>(m, x, gather, nw, W, N, K, Y, ldy, R, alpha, epi) : gemv_norm_t<bf16>(m, x, gather, nw, W, N, K, Y, ldy, R, alpha, epi))
+            return;
+    }
+    rmsnorm(m, x, add, nw, scratch, gather, R);
+    gemm(m, scratch, K, W, N, K, Y, ldy, R, alpha, epi);
+}
+
 int pick_dmax(int dim) { return dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : 256; }
 
 }  // namespace
@@ -1274,6 +1427,8 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
     {
         const char* e = getenv("B200_LP_TC");
         if (e && *e) m->use_tc = atoi(e) != 0;
+        e = getenv("B200_LP_FUSE");
+        if (e && *e) m->use_fuse = atoi(e) != 0;
         e = getenv("B200_LP_ATTN_TILE");
         if (e && *e) m->use_attn_tile = atoi(e) != 0;
         e = getenv("B200_LP_GRAPH");
@@ -1426,14 +1581,26 @@ int lp_finalize(LpModel* m, std::string* err) {
                 if ((rc = need_vec(m, l + "q.norm", a.dim, &L.qn, err))) return rc;
                 if ((rc = need_vec(m, l + "k.norm", a.dim, &L.kn, err))) return rc;
             }
-            if ((rc = need_mat(m, l + "o", W, (uint64_t)a.heads * a.vdim, &L.wo_attn, err))) return rc;
-            if ((rc = need_mat(m, r + "o", W, (uint64_t)mm.heads * mm.vdim, &L.wo_mem, err))) return rc;
+            {   // the two output projections side by side: one product [attention | memory] x [W_o attention | W_o memory]^T
+                void *wa, *wm;
+                const size_t Ka = (size_t)a.heads * a.vdim, Kb = (size_t)mm.heads * mm.vdim, es = elt(m);
+                if ((rc = need_mat(m, l + "o", W, Ka, &wa, err))) return rc;
+                if ((rc = need_mat(m, r + "o", W, Kb, &wm, err))) return rc;
+                LCU_ALLOC(cudaMalloc(&L.wo_cat, up16(W * (Ka + Kb) * es)));
+                LCU(cudaMemcpy2D(L.wo_cat, (Ka + Kb) * es, wa, Ka * es, Ka * es, W, cudaMemcpyDeviceToDevice));
+                LCU(cudaMemcpy2D((uint8_t*)L.wo_cat + Ka * es, (Ka + Kb) * es, wm, Kb * es, Kb * es, W, cudaMemcpyDeviceToDevice));
+                L.k_cat = (int)(Ka + Kb);
+                for (const std::string& nm : {l + "o", r + "o"}) {
+                    cudaFree(m->tensors[nm].d);
+                    m->tensors.erase(nm);
+                }
+            }
             if ((rc = need_vec(m, r + "norm", (uint64_t)mm.heads * mm.vdim, &L.mem_norm, err))) return rc;
             if ((rc = need_vec(m, r + "i.b", mm.heads, &L.ib, err))) return rc;
             if ((rc = need_vec(m, r + "f.b", mm.heads, &L.fb, err))) return rc;
             L.kv_bytes = up16((size_t)p.max_seq_len * a.kv_heads * (a.dim + a.vdim) * 4);
             L.rec_bytes = up16(((size_t)mm.heads * mm.dim * mm.vdim + (size_t)mm.heads * mm.dim + mm.heads) * 4);
-            m->max_act = std::max(m->max_act, std::max(a.heads * a.vdim, mm.heads * mm.vdim));
+            m->max_act = std::max(m->max_act, L.k_cat);
             m->max_o = std::max(m->max_o, mm.heads * mm.vdim);
             m->max_q = std::max(m->max_q, a.heads * a.dim);
         } else {
@@ -1513,7 +1680,10 @@ void lp_destroy(LpModel* m) {
     for (auto& kv : m->tensors) cudaFree(kv.second.d);
     for (auto& g : m->graphs)
         if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
-    for (LayerPlan& L : m->plan) cudaFree(L.w_in);
+    for (LayerPlan& L : m->plan) {
+        cudaFree(L.w_in);
+        cudaFree(L.wo_cat);
+    }
     for (SlotMem& s : m->slot) { cudaFree(s.kv); cudaFree(s.rec); }
     for (SlotMem& s : m->pool) { cudaFree(s.kv); cudaFree(s.rec); }
     for (void* ptr : {(void*)m->inv_freq, (void*)m->d_meta, (void*)m->x, (void*)m->P, (void*)m->qbuf, (void*)m->O, (void*)m->conv, (void*)m->logits,
@@ -1626,7 +1796,7 @@ bool attn_tile_launch(LpModel* m, const StepMeta& sm, const AttnGeom& ag, int ld
 }
 bool attn_tile(LpModel* m, const StepMeta& sm, const AttnGeom& ag, int ldp, int n_runs, int max_len) {
     if (m->f32 || !m->use_attn_tile || max_len < 16) return false;
-    if (ag.dim % 16 || ag.vdim % 8 || ag.dim > 128 || ag.vdim > 256 || (ag.H * ag.vdim) % 2) return false;
+    if (ag.dim % 16 || ag.vdim % 8 || ag.dim > 128 || ag.vdim > 256 || ag.out_ld % 2) return false;
     if (ag.dim <= 64 && ag.vdim <= 64) return attn_tile_launch<64, 64>(m, sm, ag, ldp, n_runs, max_len);
     if (ag.vdim <= 128) return attn_tile_launch<128, 128>(m, sm, ag, ldp, n_runs, max_len);
     return attn_tile_launch<128, 256>(m, sm, ag, ldp, n_runs, max_len);
@@ -1644,18 +1814,20 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
     for (size_t run = 0; run < m->runs.size(); run++) {
         LayerPlan& L = m->plan[m->runs[run]];
         const float* add = m->run_pass[run] >= 0 ? loop_step + (size_t)m->run_pass[run] * W : nullptr;
-        rmsnorm(m, m->x, add, L.norm1, m->hn, nullptr, R);
-        gemm(m, m->hn, W, L.w_in, L.n_in, W, m->P, L.n_in, R, 1.0f, EPI_STORE);
+        norm_gemm(m, m->x, add, nullptr, L.norm1, m->hn, L.w_in, L.n_in, m->P, L.n_in, R, 1.0f, EPI_STORE);
         if (L.d.mixer == B200_MIX_WINDOW_MEMORY) {
             AttnGeom ag = L.ag;
             ag.kv_off = m->run_kv_off[run];
-            launch(m, lp_attn_prep_kernel, dim3(R), dim3(128), 0, sm, ag, (const float*)m->P, L.n_in, L.qn, L.kn, m->qbuf);
+            ag.out_ld = L.k_cat;
+            ag.out_scale = L.d.attn_scale;
+            ag.fused_prep = (m->use_fuse && max_len == 1) ? 1 : 0;
+            if (!ag.fused_prep) launch(m, lp_attn_prep_kernel, dim3(R), dim3(128), 0, sm, ag, (const float*)m->P, L.n_in, L.qn, L.kn, m->qbuf);
             if (attn_tile(m, sm, ag, L.n_in, n_runs, max_len)) {
             } else {
             dim3 agrid(R, ag.H);
             const size_t asmem = (size_t)(((ag.dim + 3) & ~3) + ATT_WARPS * ag.vdim + 2 * ATT_WARPS) * 4;
-            if (m->f32) launch(m, lp_window_attn_kernel<float>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (float*)m->act_a);
-            else launch(m, lp_window_attn_kernel<bf16>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, (bf16*)m->act_a);
+            if (m->f32) launch(m, lp_window_attn_kernel<float>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, L.qn, L.kn, (float*)m->act_a);
+            else launch(m, lp_window_attn_kernel<bf16>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, L.qn, L.kn, (bf16*)m->act_a);
             }
             MemGeom mg = L.mg;
             mg.rec_off = m->run_rec_off[run];
@@ -1669,15 +1841,15 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                 default: launch(m, lp_matrix_memory_kernel<256>, sgrid, dim3(SCAN_BD), 0, sm, mg, (const float*)m->P, L.n_in, L.ib, L.fb, m->O, ldo); break;
             }
             dim3 hgrid(R, (mg.H + 3) / 4);
-            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (float*)m->act_b, R);
-            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (bf16*)m->act_b, R);
-            gemm(m, m->act_a, ag.H * ag.vdim, L.wo_attn, W, ag.H * ag.vdim, m->x, W, R, L.d.attn_scale, EPI_ADD);
-            gemm(m, m->act_b, ldo, L.wo_mem, W, ldo, m->x, W, R, L.d.mem_scale, EPI_ADD);
+            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (float*)m->act_a + ag.H * ag.vdim, L.k_cat, L.d.mem_scale, R);
+            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (bf16*)m->act_a + ag.H * ag.vdim, L.k_cat, L.d.mem_scale, R);
+            gemm(m, m->act_a, L.k_cat, L.wo_cat, W, L.k_cat, m->x, W, R, 1.0f, EPI_ADD);
         } else {
             DeltaGeom dg = L.dg;
             dg.rec_off = m->run_rec_off[run];
-            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, m->conv);
-            if (dg.taps > 1) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
+            const int shift = (m->use_fuse && max_len == 1) ? 1 : 0;
+            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, m->conv, shift);
+            if (dg.taps > 1 && !shift) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
             const int ldo = dg.H * dg.vdim;
             const int dcols = SCAN_BD / (pick_dmax(dg.dim) / SCAN_DREG);
             dim3 sgrid((dg.vdim + dcols - 1) / dcols, dg.H, n_runs);
@@ -1688,20 +1860,19 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                 default: launch(m, lp_gated_delta_kernel<256>, sgrid, dim3(SCAN_BD), 0, sm, dg, (const float*)m->conv, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, m->O, ldo); break;
             }
             dim3 hgrid(R, (dg.H + 3) / 4);
-            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (float*)m->act_a, R);
-            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (bf16*)m->act_a, R);
+            if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (float*)m->act_a, ldo, 1.0f, R);
+            else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (bf16*)m->act_a, ldo, 1.0f, R);
             gemm(m, m->act_a, ldo, L.wo_delta, W, ldo, m->x, W, R, 1.0f, EPI_ADD);
         }
         if (L.d.ff > 0) {
-            rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
-            gemm(m, m->hn, W, L.w_up, L.d.ff, W, m->act_a, L.d.ff, R, 1.0f, EPI_RELU2);
+            norm_gemm(m, m->x, nullptr, nullptr, L.norm2, m->hn, L.w_up, L.d.ff, m->act_a, L.d.ff, R, 1.0f, EPI_RELU2);
             gemm(m, m->act_a, L.d.ff, L.w_down, W, L.d.ff, m->x, W, R, 1.0f, EPI_ADD);
         }
         if (taps_len > 0) cudaMemcpyAsync(m->taps + run * (size_t)taps_len * W, m->x, (size_t)taps_len * W * 4, cudaMemcpyDeviceToDevice, m->stream);
     }
     if (head) {
-        rmsnorm(m, m->x, nullptr, (const float*)find(m, "final.norm")->d, m->hw, sm.want, n_want);
-        gemm(m, m->hw, W, find(m, "head")->d, p.vocab, W, m->logits, p.vocab, n_want, p.logit_scale, EPI_STORE);
+        norm_gemm(m, m->x, nullptr, sm.want, (const float*)find(m, "final.norm")->d, m->hw, find(m, "head")->d, p.vocab, m->logits, p.vocab, n_want,
+                  p.logit_scale, EPI_STORE);
         if (head == 2) launch(m, lp_argmax_kernel, dim3(n_want), dim3(1024), 0, (const float*)m->logits, p.vocab, m->pick);
     }
 }

@@ -432,3 +432,30 @@ def test_tile_attention_against_warp_attention(b200, monkeypatch, dims):
     assert S.rel_err(outs["1"], outs["0"]) < 2e-2
     assert S.rel_err(outs["1"], want) < BF16_TOL
     assert S.rel_err(outs["0"], want) < BF16_TOL
+
+
+def test_fused_decode_kernels_against_unfused(b200, monkeypatch):
+    # decoding takes fused kernels (norm inside the projection, q/k norm and the cache write inside attention, the convolution
+    # tail moved on by the convolution itself); B200_LP_FUSE=0 runs every step as its own kernel.  Both against the oracle, in a
+    # batch whose members sit at different positions, f32 mode.
+    cfg = S.config([S.parallel_layer(heads=4, kv_heads=2, dim=24, vdim=40, window=7, keep_first=2), S.delta_layer(conv=4, ff=56),
+                    S.parallel_layer(heads=2, kv_heads=2, dim=16, vdim=24, window=30, keep_first=0, ff=0)], loop=(0, 2, 2))
+    w = S.random_weights(cfg, 53)
+    ref = O.Model(cfg, w)
+    prompts = [tokens(n, cfg["vocab"], 60 + n) for n in (3, 19, 1)]
+    tails = [tokens(12, cfg["vocab"], 70 + i) for i in range(3)]
+    states = [ref.new_state() for _ in prompts]
+    for st, pr in zip(states, prompts):
+        ref.step(st, pr)
+    want = [[ref.step(states[i], [tails[i][k]])[0] for i in range(3)] for k in range(12)]
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("B200_LP_FUSE", fuse)
+        gpu = S.gpu_model(cfg, w)
+        try:
+            gpu.step([(i, pr) for i, pr in enumerate(prompts)])
+            for k in range(12):
+                lg = gpu.decode_batch([0, 1, 2], [tails[i][k] for i in range(3)])
+                for i in range(3):
+                    assert S.rel_err(lg[i], want[k][i]) < F32_TOL, (fuse, k, i)
+        finally:
+            gpu.close()
