@@ -364,6 +364,7 @@ __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, i
         const int nr = min(GV_ROWS, R - rb);
         float acc[GV_ROWS] = {};
         if (vec_ok) {
+#pragma unroll 4
             for (int k = lane * VN; k < K; k += 32 * VN) {
                 float wv[VN], xv[VN];
                 Vec8<T>::load(wr + k, wv);
@@ -431,6 +432,7 @@ __global__ void __launch_bounds__(256) lp_gemv_norm_kernel(const float* __restri
     for (int rb = 0; rb < R; rb += GV_ROWS) {
         const int nr = min(GV_ROWS, R - rb);
         float acc[GV_ROWS] = {};
+#pragma unroll 4
         for (int k = lane * VN; k < K; k += 32 * VN) {   // (K is a multiple of VN: checked by the host)
             float wv[VN], xv[VN];
             Vec8<T>::load(wr + k, wv);
@@ -560,23 +562,31 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
         if (v4) {
             // lanes split the key channels (coalesced 16-byte loads of one cache row per key), a butterfly sums the partial dots
             const int cnt = min(32, end - j0);
-#pragma unroll 8
-            for (int jj = 0; jj < cnt; jj++) {
-                const float* kr = kc + (size_t)(j0 + jj) * ldk + g * a.dim;
-                float part = 0.0f;
+            for (int jb = 0; jb < cnt; jb += 8) {      // eight keys at a time: all their loads first, then the eight butterflies
+                float part[8];
 #pragma unroll
-                for (int c = 0; c < ATT_QCH; c++) {
-                    const int d = (lane + 32 * c) * 4;
-                    if (d < a.dim) {
-                        const float4 kv = *reinterpret_cast<const float4*>(kr + d);
-                        part = fmaf(qr[c].x, kv.x, part);
-                        part = fmaf(qr[c].y, kv.y, part);
-                        part = fmaf(qr[c].z, kv.z, part);
-                        part = fmaf(qr[c].w, kv.w, part);
+                for (int u = 0; u < 8; u++) {
+                    part[u] = 0.0f;
+                    if (jb + u < cnt) {
+                        const float* kr = kc + (size_t)(j0 + jb + u) * ldk + g * a.dim;
+#pragma unroll
+                        for (int c = 0; c < ATT_QCH; c++) {
+                            const int d = (lane + 32 * c) * 4;
+                            if (d < a.dim) {
+                                const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+                                part[u] = fmaf(qr[c].x, kv.x, part[u]);
+                                part[u] = fmaf(qr[c].y, kv.y, part[u]);
+                                part[u] = fmaf(qr[c].z, kv.z, part[u]);
+                                part[u] = fmaf(qr[c].w, kv.w, part[u]);
+                            }
+                        }
                     }
                 }
-                part = wsum(part);
-                if (lane == jj) s = part * a.scale;
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const float tot = wsum(part[u]);
+                    if (lane == jb + u && jb + u < cnt) s = tot * a.scale;
+                }
             }
         } else if (j < end) {
             const float* kr = kc + (size_t)j * ldk + g * a.dim;
@@ -592,15 +602,25 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
 #pragma unroll
         for (int c = 0; c < ATT_ACC; c++) acc[c] *= corr;
         const int cnt = min(32, end - j0);
-#pragma unroll 8
-        for (int jj = 0; jj < cnt; jj++) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const float* vr = vc + (size_t)(j0 + jj) * ldv + g * a.vdim;
+        for (int jb = 0; jb < cnt; jb += 4) {          // four value rows at a time: weights first, then all loads, then the sums
+            float pj[4];
 #pragma unroll
-            for (int c = 0; c < ATT_ACC; c++) {
-                const int ch = c * 32 + lane;
-                if (ch < a.vdim) acc[c] = fmaf(pj, vr[ch], acc[c]);
+            for (int u = 0; u < 4; u++) pj[u] = __shfl_sync(0xffffffffu, p, (jb + u) & 31);
+            float vv[4][ATT_ACC];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float* vr = vc + (size_t)(j0 + min(jb + u, cnt - 1)) * ldv + g * a.vdim;
+#pragma unroll
+                for (int c = 0; c < ATT_ACC; c++) {
+                    const int ch = c * 32 + lane;
+                    vv[u][c] = ch < a.vdim ? vr[ch] : 0.0f;
+                }
+                if (jb + u >= cnt) pj[u] = 0.0f;
             }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int c = 0; c < ATT_ACC; c++) acc[c] = fmaf(pj[u], vv[u][c], acc[c]);
         }
     }
 #pragma unroll
