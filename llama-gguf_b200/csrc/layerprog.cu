@@ -836,10 +836,11 @@ struct MemGeom {
     int q_off, k_off, v_off, i_off, f_off;
     size_t rec_off;
 };
-constexpr int SCAN_BD = 64, SCAN_DREG = 32;
-// How the scans are laid out.  A state column S[:, j] is cut into pieces of SCAN_DREG = 32 key channels, one piece per thread in
-// registers: DMAX / 32 neighbouring lanes share a column (partial dot products meet through shuffles) and a block of 64 threads covers
-// 64 / (DMAX / 32) columns, so wide keys mean more blocks and a shorter serial chain per token, not more registers.  Tokens are staged
+constexpr int SCAN_BD = 64, SCAN_DREG = 16;
+// How the scans are laid out.  A state column S[:, j] is cut into pieces of SCAN_DREG = 16 key channels, one piece per thread in
+// registers (groups of four channels dealt round robin, so that the lanes of a column read neighbouring 16-byte words of shared
+// memory): DMAX / 16 neighbouring lanes share a column (partial dot products meet through shuffles) and a block of 64 threads covers
+// 64 / (DMAX / 16) columns, so wide keys mean more blocks and a shorter serial chain per token, not more registers.  Tokens are staged
 // SCAN_CH at a time with 4-byte cp.async copies (all in flight together: one global round trip per chunk), gates and unit norms are
 // worked out one token per thread / warp, and the serial loop over the chunk's tokens runs out of shared memory and registers.
 template <int DMAX> struct ScanChunk { static constexpr int N = DMAX > 128 ? 16 : 32; };
@@ -861,7 +862,7 @@ __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, 
     __shared__ __align__(16) float qs[CH][DMAX];
     __shared__ __align__(16) float ks[CH][DMAX];
     __shared__ float vs[CH][COLS], il_s[CH], fl_s[CH];
-    const int tid = threadIdx.x, lane = tid & 31, col = tid / SPLIT, d0 = (tid % SPLIT) * SCAN_DREG;
+    const int tid = threadIdx.x, lane = tid & 31, col = tid / SPLIT, sub = tid % SPLIT;
     const int j = blockIdx.x * COLS + col, h = blockIdx.y, run = blockIdx.z;
     const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
     float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
@@ -870,7 +871,10 @@ __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, 
     const bool live = j < g.vdim;
     float s[SCAN_DREG];
 #pragma unroll
-    for (int i = 0; i < SCAN_DREG; i++) s[i] = (live && d0 + i < g.dim) ? Sg[(size_t)(d0 + i) * g.vdim + j] : 0.0f;
+    for (int i = 0; i < SCAN_DREG; i++) {
+        const int d = ((i >> 2) * SPLIT + sub) * 4 + (i & 3);   // channel of register i
+        s[i] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
+    }
     float nreg[DMAX / 32];   // n, element lane + 32 i (every warp keeps its own copy)
 #pragma unroll
     for (int i = 0; i < DMAX / 32; i++) nreg[i] = lane + 32 * i < g.dim ? ng[lane + 32 * i] : 0.0f;
@@ -912,8 +916,8 @@ __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, 
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
             for (int i = 0; i < SCAN_DREG; i += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d0 + i]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][d0 + i]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][((i >> 2) * SPLIT + sub) * 4]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][((i >> 2) * SPLIT + sub) * 4]);
                 s[i] = fmaf(fa, s[i], k4.x * iv);
                 s[i + 1] = fmaf(fa, s[i + 1], k4.y * iv);
                 s[i + 2] = fmaf(fa, s[i + 2], k4.z * iv);
@@ -931,13 +935,15 @@ __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, 
             }
             nq = wsum(nq) * qscale;
             const float acc = split_sum<SPLIT>((a0 + a1) + (a2 + a3)) * qscale;
-            if (live && d0 == 0) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = acc / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+            if (live && sub == 0) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = acc / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
         }
     }
     if (live)
 #pragma unroll
-        for (int i = 0; i < SCAN_DREG; i++)
-            if (d0 + i < g.dim) Sg[(size_t)(d0 + i) * g.vdim + j] = s[i];
+        for (int i = 0; i < SCAN_DREG; i++) {
+            const int d = ((i >> 2) * SPLIT + sub) * 4 + (i & 3);
+            if (d < g.dim) Sg[(size_t)d * g.vdim + j] = s[i];
+        }
     if (blockIdx.x == 0 && tid < 32) {
 #pragma unroll
         for (int i = 0; i < DMAX / 32; i++)
@@ -997,7 +1003,7 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
     __shared__ __align__(16) float qs[CH][DMAX];
     __shared__ __align__(16) float ks[CH][DMAX];
     __shared__ float vs[CH][COLS], beta_s[CH], dec_s[CH];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, col = tid / SPLIT, d0 = (tid % SPLIT) * SCAN_DREG;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, col = tid / SPLIT, sub = tid % SPLIT;
     const int j = blockIdx.x * COLS + col, h = blockIdx.y, run = blockIdx.z;
     const int hk = h / (g.H / g.G);
     const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
@@ -1005,7 +1011,10 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
     const bool live = j < g.vdim;
     float s[SCAN_DREG];
 #pragma unroll
-    for (int i = 0; i < SCAN_DREG; i++) s[i] = (live && d0 + i < g.dim) ? Sg[(size_t)(d0 + i) * g.vdim + j] : 0.0f;
+    for (int i = 0; i < SCAN_DREG; i++) {
+        const int d = ((i >> 2) * SPLIT + sub) * 4 + (i & 3);   // channel of register i
+        s[i] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
+    }
     for (int i = tid; i < CH * DMAX; i += SCAN_BD) {
         (&qs[0][0])[i] = 0.0f;
         (&ks[0][0])[i] = 0.0f;
@@ -1049,7 +1058,7 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
             float k0 = 0.0f, k1 = 0.0f, k2 = 0.0f, k3 = 0.0f;
 #pragma unroll
             for (int i = 0; i < SCAN_DREG; i += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d0 + i]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][((i >> 2) * SPLIT + sub) * 4]);
                 s[i] *= decay;
                 s[i + 1] *= decay;
                 s[i + 2] *= decay;
@@ -1063,8 +1072,8 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
             for (int i = 0; i < SCAN_DREG; i += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][d0 + i]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][d0 + i]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][((i >> 2) * SPLIT + sub) * 4]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][((i >> 2) * SPLIT + sub) * 4]);
                 s[i] = fmaf(k4.x, u, s[i]);
                 s[i + 1] = fmaf(k4.y, u, s[i + 1]);
                 s[i + 2] = fmaf(k4.z, u, s[i + 2]);
@@ -1075,13 +1084,15 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
                 a3 = fmaf(s[i + 3], q4.w, a3);
             }
             const float acc = split_sum<SPLIT>((a0 + a1) + (a2 + a3));
-            if (live && d0 == 0) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = acc;
+            if (live && sub == 0) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = acc;
         }
     }
     if (live)
 #pragma unroll
-        for (int i = 0; i < SCAN_DREG; i++)
-            if (d0 + i < g.dim) Sg[(size_t)(d0 + i) * g.vdim + j] = s[i];
+        for (int i = 0; i < SCAN_DREG; i++) {
+            const int d = ((i >> 2) * SPLIT + sub) * 4 + (i & 3);
+            if (d < g.dim) Sg[(size_t)d * g.vdim + j] = s[i];
+        }
 }
 
 // out[r][h][c] = o / sqrt(mean_c o^2 + eps) * w[w_per_head ? c : h * vdim + c] * act(gate), act = sigmoid (0) or SiLU (1); one warp
@@ -1314,7 +1325,7 @@ bool tc_gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, vo
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
     if (R <= 64) return tc_launch<64>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);
-    if (R <= 128 || (long long)((N + TC_M - 1) / TC_M) * ((R + 255) / 256) < 148) return tc_launch<128>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);
+    if (R <= 128) return tc_launch<128>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);   // (wider token tiles move fewer operand bytes per FLOP: measured 2.5x on a 2048 x 8192 x 2048 product even at 128 CTAs)
     return tc_launch<256>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);
 }
 

@@ -61,9 +61,9 @@ def tensor_shapes(cfg):
     """name -> shape of every tensor a model of this config holds (what model.safetensors must contain)."""
     W, V = cfg["width"], cfg["vocab"]
     out = {"embed": (V, W), "head": (V, W), "final.norm": (W,)}
-    lp = cfg["loop"]
-    if lp["stop"] > lp["start"]:
-        out["loop.step"] = (lp["times"], W)
+    lp = cfg.get("loop") or {}
+    if lp.get("stop", 0) > lp.get("start", 0):
+        out["loop.step"] = (lp.get("times", 1), W)
     for i, L in enumerate(cfg["layers"]):
         p, m = "l%d." % i, L["mixer"]
         out[p + "norm1"] = (W,)
@@ -83,7 +83,7 @@ def tensor_shapes(cfg):
             out.update({x + "q": (qk, W), x + "q.conv": (qk, m["conv"]), x + "k": (qk, W), x + "k.conv": (qk, m["conv"]),
                         x + "v": (vv, W), x + "v.conv": (vv, m["conv"]), x + "b": (m["heads"], W), x + "A_log": (m["heads"],),
                         x + "norm": (m["vdim"],), x + "a": (m["heads"], W), x + "dt_bias": (m["heads"],), x + "g": (vv, W), x + "o": (W, vv)})
-        if L["mlp"]:
+        if L.get("mlp"):
             out.update({p + "norm2": (W,), p + "mlp.up": (L["mlp"]["ff"], W), p + "mlp.down": (W, L["mlp"]["ff"])})
     return out
 
