@@ -354,11 +354,22 @@ template <> struct Vec8<float> {
 };
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int ldw, void* __restrict__ Y,
-                                                      int ldy, int R, int N, int K, float alpha, int vec_ok) {
-    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+                                                      int ldy, int R, int N, int K, float alpha, int vec_ok, int stage) {
+    extern __shared__ __align__(16) uint8_t gv_smem[];
     const int lane = threadIdx.x & 31;
-    if (n >= N) return;
     constexpr int VN = Vec8<T>::N;
+    if (stage) {   // the activation rows once per block into shared memory (every warp of the block reads all of them)
+        T* xs = reinterpret_cast<T*>(gv_smem);
+        const int per_row = K / VN;
+        for (int i = threadIdx.x; i < R * per_row; i += blockDim.x) {
+            const int r = i / per_row, c = i - r * per_row;
+            *reinterpret_cast<uint4*>(xs + (size_t)r * K + c * VN) = *reinterpret_cast<const uint4*>(X + (size_t)r * ldx + c * VN);
+        }
+        __syncthreads();
+        X = xs;
+        ldx = K;
+    }
+    for (int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); n < N; n += gridDim.x * (blockDim.x >> 5)) {
     const T* wr = W + (size_t)n * ldw;
     for (int rb = 0; rb < R; rb += GV_ROWS) {
         const int nr = min(GV_ROWS, R - rb);
@@ -393,6 +404,7 @@ __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, i
             }
         }
     }
+    }
 }
 
 // The same for a normed input: the block first norms the (few) rows of the f32 residual stream into shared memory -- rms over the
@@ -425,9 +437,8 @@ __global__ void __launch_bounds__(256) lp_gemv_norm_kernel(const float* __restri
         for (int k = threadIdx.x; k < K; k += 256) xs[(size_t)r * K + k] = from_f<T>(xr[k] * inv * nw[k]);
     }
     __syncthreads();
-    const int n = blockIdx.x * 8 + warp;
-    if (n >= N) return;
     constexpr int VN = Vec8<T>::N;
+    for (int n = blockIdx.x * 8 + warp; n < N; n += gridDim.x * 8) {
     const T* wr = W + (size_t)n * K;
     for (int rb = 0; rb < R; rb += GV_ROWS) {
         const int nr = min(GV_ROWS, R - rb);
@@ -452,6 +463,7 @@ __global__ void __launch_bounds__(256) lp_gemv_norm_kernel(const float* __restri
                 if (lane == 0) epi_store<T, EPI>(Y, (size_t)(rb + i) * ldy + n, alpha * sum);
             }
         }
+    }
     }
 }
 
@@ -496,10 +508,10 @@ __global__ void lp_attn_prep_kernel(StepMeta sm, AttnGeom a, const float* __rest
 // scores (q from shared memory), online softmax in f32 per warp, then the block's 32 value rows are added lane-per-channel; the
 // warps' partial (max, sum, output) triples are merged through shared memory.  Visible keys of position i: [0, min(keep_first, lo))
 // and [lo, i], lo = max(0, i - window + 1).  The output is multiplied by sigmoid(gate) when the layer has an output gate.
-constexpr int ATT_ACC = 16;   // value channels per lane: vdim <= 512
-constexpr int ATT_WARPS = 8;
+constexpr int ATT_ACC = 16;   // value channels per lane at most: vdim <= 512 (the kernel is instantiated for 4, 8 and 16)
+constexpr int ATT_WARPS = 16;
 constexpr int ATT_QCH = 2;    // 16-byte query chunks per lane in the split-channel score loop: dim <= 256 (wider: one key per lane)
-template <typename OutT>
+template <typename OutT, int VCH>
 __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta sm, AttnGeom a, const float* __restrict__ qbuf,
                                                                         const float* __restrict__ P, int ldp, const float* __restrict__ qw,
                                                                         const float* __restrict__ kw, OutT* __restrict__ out) {
@@ -544,9 +556,9 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
     const int a_end = min(a.keep_first, lo);
     const int nb0 = (a_end + 31) >> 5, nb1 = (i + 1 - lo + 31) >> 5;
     float m = -INFINITY, l = 0.0f;
-    float acc[ATT_ACC];
+    float acc[VCH];
 #pragma unroll
-    for (int c = 0; c < ATT_ACC; c++) acc[c] = 0.0f;
+    for (int c = 0; c < VCH; c++) acc[c] = 0.0f;
     const bool v4 = (a.dim & 3) == 0 && a.dim <= 128 * ATT_QCH;
     float4 qr[ATT_QCH];
 #pragma unroll
@@ -600,31 +612,32 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
         l = l * corr + wsum(p);
         m = m_new;
 #pragma unroll
-        for (int c = 0; c < ATT_ACC; c++) acc[c] *= corr;
+        for (int c = 0; c < VCH; c++) acc[c] *= corr;
         const int cnt = min(32, end - j0);
-        for (int jb = 0; jb < cnt; jb += 4) {          // four value rows at a time: weights first, then all loads, then the sums
-            float pj[4];
+        constexpr int PVB = VCH <= 4 ? 8 : 4;          // value rows per batch: weights first, then all loads, then the sums
+        for (int jb = 0; jb < cnt; jb += PVB) {
+            float pj[PVB];
 #pragma unroll
-            for (int u = 0; u < 4; u++) pj[u] = __shfl_sync(0xffffffffu, p, (jb + u) & 31);
-            float vv[4][ATT_ACC];
+            for (int u = 0; u < PVB; u++) pj[u] = __shfl_sync(0xffffffffu, p, (jb + u) & 31);
+            float vv[PVB][VCH];
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < PVB; u++) {
                 const float* vr = vc + (size_t)(j0 + min(jb + u, cnt - 1)) * ldv + g * a.vdim;
 #pragma unroll
-                for (int c = 0; c < ATT_ACC; c++) {
+                for (int c = 0; c < VCH; c++) {
                     const int ch = c * 32 + lane;
                     vv[u][c] = ch < a.vdim ? vr[ch] : 0.0f;
                 }
                 if (jb + u >= cnt) pj[u] = 0.0f;
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++)
+            for (int u = 0; u < PVB; u++)
 #pragma unroll
-                for (int c = 0; c < ATT_ACC; c++) acc[c] = fmaf(pj[u], vv[u][c], acc[c]);
+                for (int c = 0; c < VCH; c++) acc[c] = fmaf(pj[u], vv[u][c], acc[c]);
         }
     }
 #pragma unroll
-    for (int c = 0; c < ATT_ACC; c++) {
+    for (int c = 0; c < VCH; c++) {
         const int ch = c * 32 + lane;
         if (ch < a.vdim) acc_s[warp * a.vdim + ch] = acc[c];
     }
@@ -1337,10 +1350,14 @@ void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int N, int K, voi
     if (R <= 2 * GV_ROWS) {
         constexpr int VN = Vec8<T>::N;
         const int vec_ok = (K % VN == 0 && ldx % VN == 0 && ((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0) ? 1 : 0;
-        dim3 grid((N + 7) / 8), block(256);
-        if (epi == EPI_STORE) launch(m, lp_gemv_kernel<T, EPI_STORE>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok);
-        else if (epi == EPI_ADD) launch(m, lp_gemv_kernel<T, EPI_ADD>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok);
-        else launch(m, lp_gemv_kernel<T, EPI_RELU2>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok);
+        // a few blocks per SM, each walking its share of the output columns with the activation rows staged once
+        dim3 grid(std::min((N + 7) / 8, 4 * 148)), block(256);
+        const size_t xbytes = (size_t)R * K * sizeof(T);
+        const int stage = (vec_ok && sizeof(T) * VN == 16 && xbytes <= 48 * 1024) ? 1 : 0;
+        const size_t smem = stage ? xbytes : 0;
+        if (epi == EPI_STORE) launch(m, lp_gemv_kernel<T, EPI_STORE>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok, stage);
+        else if (epi == EPI_ADD) launch(m, lp_gemv_kernel<T, EPI_ADD>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok, stage);
+        else launch(m, lp_gemv_kernel<T, EPI_RELU2>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok, stage);
         return;
     }
     if (tc_gemm(m, X, ldx, W, N, K, Y, ldy, R, alpha, epi)) return;
@@ -1380,7 +1397,7 @@ bool gemv_norm_t(LpModel* m, const float* x, const int* gather, const float* nw,
         if (dev >= 0 && dev < 64) once[e][dev] = true;
         return true;
     };
-    dim3 grid((N + 7) / 8), block(256);
+    dim3 grid(std::min((N + 7) / 8, 4 * 148)), block(256);
     const T* w = (const T*)W;
     if (epi == EPI_STORE) {
         if (!prep(lp_gemv_norm_kernel<T, EPI_STORE>, 0)) return false;
@@ -1857,8 +1874,14 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             } else {
             dim3 agrid(R, ag.H);
             const size_t asmem = (size_t)(((ag.dim + 3) & ~3) + ATT_WARPS * ag.vdim + 2 * ATT_WARPS) * 4;
-            if (m->f32) launch(m, lp_window_attn_kernel<float>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, L.qn, L.kn, (float*)m->act_a);
-            else launch(m, lp_window_attn_kernel<bf16>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, L.qn, L.kn, (bf16*)m->act_a);
+            const int vch = ag.vdim <= 128 ? 4 : ag.vdim <= 256 ? 8 : 16;
+#define LP_ATTN(T, V) launch(m, lp_window_attn_kernel<T, V>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, L.qn, L.kn, (T*)m->act_a)
+            if (m->f32) {
+                if (vch == 4) LP_ATTN(float, 4); else if (vch == 8) LP_ATTN(float, 8); else LP_ATTN(float, 16);
+            } else {
+                if (vch == 4) LP_ATTN(bf16, 4); else if (vch == 8) LP_ATTN(bf16, 8); else LP_ATTN(bf16, 16);
+            }
+#undef LP_ATTN
             }
             MemGeom mg = L.mg;
             mg.rec_off = m->run_rec_off[run];
