@@ -251,7 +251,8 @@ B200_API const char* b200_batch_last_error(b200_batch* batch);   /* message of t
  * Mixers (csrc/layerprog.cu; all constants are fields, nothing is fixed to one model):
  *   B200_MIX_WINDOW_MEMORY  two branches on the same normed input, summed with attn_scale / mem_scale:
  *        - softmax attention over a sliding window that also keeps the first `keep_first` positions visible
- *          (key j visible from i iff j <= i and (i - j < window or j < keep_first)), grouped K/V heads, optional per-head RMS
+ *          (key j visible from i iff j <= i and (i - j < window or j < keep_first)), grouped K/V heads (query head h reads K/V
+ *          head floor(h * kv_heads / heads)), optional per-head RMS
  *          norm of q and k (qk_norm), no rotation, optional sigmoid output gate (out_gate), separate q/k and v head sizes;
  *        - a matrix memory with exponential input gate, sigmoid forget gate (both soft-capped: cap * tanh(z / cap)) and a
  *          running-maximum stabiliser that starts at 0; read-out normalised by max(|n.q|, exp(-m)) + 1e-6, per-head unit RMS,

@@ -521,7 +521,7 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
     float* ml_s = acc_s + ATT_WARPS * a.vdim;          // [ATT_WARPS][2]
     const int r = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int run = sm.row_run[r], i = sm.row_pos[r];
-    const int g = h / (a.H / a.G);
+    const int g = h * a.G / a.H;
     const float* kc = reinterpret_cast<const float*>(sm.run_kv[run] + a.kv_off);
     const float* vc = kc + (size_t)a.cap * a.G * a.dim;
     const int ldk = a.G * a.dim, ldv = a.G * a.vdim;
@@ -694,7 +694,7 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
     const int r0 = sm.run_start[run], len = sm.run_start[run + 1] - r0, p0 = sm.run_pos0[run];
     const int t0 = blockIdx.x * AT_Q;
     if (t0 >= len) return;
-    const int g = h / (a.H / a.G);
+    const int g = h * a.G / a.H;
     const float* kc = reinterpret_cast<const float*>(sm.run_kv[run] + a.kv_off);
     const float* vc = kc + (size_t)a.cap * a.G * a.dim;
     const int ldk = a.G * a.dim, ldv = a.G * a.vdim;
@@ -1018,7 +1018,7 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
     __shared__ float vs[CH][COLS], beta_s[CH], dec_s[CH];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, col = tid / SPLIT, sub = tid % SPLIT;
     const int j = blockIdx.x * COLS + col, h = blockIdx.y, run = blockIdx.z;
-    const int hk = h / (g.H / g.G);
+    const int hk = h * g.G / g.H;
     const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
     float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
     const bool live = j < g.vdim;
@@ -1439,14 +1439,14 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
         if (L.mixer == B200_MIX_WINDOW_MEMORY) {
             const b200_window_attn_desc& a = L.attn;
             const b200_matrix_memory_desc& mm = L.mem;
-            if (a.heads <= 0 || a.kv_heads <= 0 || a.dim <= 0 || a.vdim <= 0 || a.heads % a.kv_heads) return bad(at + "bad attention head counts or sizes");
+            if (a.heads <= 0 || a.kv_heads <= 0 || a.dim <= 0 || a.vdim <= 0 || a.kv_heads > a.heads) return bad(at + "bad attention head counts or sizes");
             if (a.window <= 0 || a.keep_first < 0) return bad(at + "window must be positive, keep_first non-negative");
             if (a.vdim > 32 * ATT_ACC) return bad(at + "attention value size above " + std::to_string(32 * ATT_ACC));
             if (mm.heads <= 0 || mm.dim <= 0 || mm.vdim <= 0 || !(mm.gate_cap > 0.0f)) return bad(at + "bad matrix-memory sizes");
             if (mm.dim > 256) return bad(at + "matrix-memory key size above 256");
         } else if (L.mixer == B200_MIX_GATED_DELTA) {
             const b200_gated_delta_desc& g = L.delta;
-            if (g.heads <= 0 || g.kv_heads <= 0 || g.dim <= 0 || g.vdim <= 0 || g.heads % g.kv_heads || g.conv < 1) return bad(at + "bad delta-rule sizes");
+            if (g.heads <= 0 || g.kv_heads <= 0 || g.dim <= 0 || g.vdim <= 0 || g.kv_heads > g.heads || g.conv < 1) return bad(at + "bad delta-rule sizes");
             if (g.dim > 256) return bad(at + "delta-rule key size above 256");
         } else return bad(at + "unknown mixer");
         if (L.ff < 0) return bad(at + "negative feed-forward width");

@@ -58,7 +58,7 @@ def windowed_attention(q, k, v, q_pos, k_pos, scale, size, keep_first):
     for a in range(Tq):
         js = [b for b in range(k.shape[0]) if visible(q_pos[a], k_pos[b], size, keep_first)]
         for h in range(H):
-            g = h // (H // G)
+            g = h * G // H                     # = floor(h / (H / G))
             s = np.array([q[a, h] @ k[b, g] for b in js]) * scale
             p = np.exp(s - s.max())
             p /= p.sum()
@@ -186,7 +186,7 @@ class Model:
         g = np.exp(-np.exp(w[p + "A_log"]) * softplus(h @ w[p + "a"].T + w[p + "dt_bias"]))
         o = np.zeros((T, H, dv))
         for hh in range(H):
-            gg = hh // (H // G)
+            gg = hh * G // H
             S = rs["S"][hh]
             for t in range(T):
                 S, o[t, hh] = delta_step(S, q[t, gg], k[t, gg], v[t, hh], beta[t, hh], g[t, hh])
