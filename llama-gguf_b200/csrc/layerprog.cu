@@ -1204,7 +1204,7 @@ struct LpModel {
     uint8_t* d_meta = nullptr;
     size_t meta_bytes = 0;
     float *x = nullptr, *P = nullptr, *qbuf = nullptr, *O = nullptr, *conv = nullptr, *logits = nullptr;
-    void *hn = nullptr, *act_a = nullptr, *act_b = nullptr, *hw = nullptr;
+    void *hn = nullptr, *act_a = nullptr, *hw = nullptr;
     int* pick = nullptr;
     float* h_logits = nullptr;          // pinned
     size_t h_logits_bytes = 0;
@@ -1735,7 +1735,7 @@ void lp_destroy(LpModel* m) {
     for (SlotMem& s : m->slot) { cudaFree(s.kv); cudaFree(s.rec); }
     for (SlotMem& s : m->pool) { cudaFree(s.kv); cudaFree(s.rec); }
     for (void* ptr : {(void*)m->inv_freq, (void*)m->d_meta, (void*)m->x, (void*)m->P, (void*)m->qbuf, (void*)m->O, (void*)m->conv, (void*)m->logits,
-                      m->hn, m->act_a, m->act_b, m->hw, (void*)m->pick, (void*)m->taps})
+                      m->hn, m->act_a, m->hw, (void*)m->pick, (void*)m->taps})
         cudaFree(ptr);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_logits) cudaFreeHost(m->h_logits);
@@ -1801,7 +1801,6 @@ int ensure_scratch(LpModel* m, int R, int n_runs, int n_want, std::string* err) 
         if ((rc = grow(&m->conv, (size_t)cap * std::max(m->max_conv, 1) * 4, err))) return rc;
         if ((rc = grow(&m->hn, (size_t)cap * W * es, err))) return rc;
         if ((rc = grow(&m->act_a, (size_t)cap * m->max_act * es, err))) return rc;
-        if ((rc = grow(&m->act_b, (size_t)cap * m->max_act * es, err))) return rc;
         m->cap_rows = cap;
     }
     if (n_want > m->cap_want) {
