@@ -726,23 +726,50 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
         for (int j0 = beg; j0 < end; j0 += AT_K) {
             const int nk = min(AT_K, end - j0);
             __syncthreads();   // the previous tile has been consumed
-            for (int i = threadIdx.x; i < AT_K * (DK / 4); i += 128) {
-                const int key = i / (DK / 4), d = (i - key * (DK / 4)) * 4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (key < nk && d < a.dim) v = *reinterpret_cast<const float4*>(kc + (size_t)(j0 + key) * ldk + g * a.dim + d);
-                uint2 w;
-                w.x = pack_bf2(v.x, v.y);
-                w.y = pack_bf2(v.z, v.w);
-                *reinterpret_cast<uint2*>(Ks + key * KS + d) = w;
+            // K: a thread takes 4 channels of one key per round (coalesced rows), all loads of a batch before their stores
+            {
+                constexpr int KN = AT_K * (DK / 4) / 128;          // 16-byte loads per thread
+#pragma unroll
+                for (int b0 = 0; b0 < KN; b0 += 8) {
+                    float4 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int i = threadIdx.x + (b0 + u) * 128, key = i / (DK / 4), d = (i - key * (DK / 4)) * 4;
+                        v[u] = (key < nk && d < a.dim) ? *reinterpret_cast<const float4*>(kc + (size_t)(j0 + key) * ldk + g * a.dim + d)
+                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int i = threadIdx.x + (b0 + u) * 128, key = i / (DK / 4), d = (i - key * (DK / 4)) * 4;
+                        uint2 w;
+                        w.x = pack_bf2(v[u].x, v[u].y);
+                        w.y = pack_bf2(v[u].z, v[u].w);
+                        *reinterpret_cast<uint2*>(Ks + key * KS + d) = w;
+                    }
+                }
             }
-            for (int i = threadIdx.x; i < AT_K * (DV / 4); i += 128) {
-                const int key = i / (DV / 4), c = (i - key * (DV / 4)) * 4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (key < nk && c < a.vdim) v = *reinterpret_cast<const float4*>(vc + (size_t)(j0 + key) * ldv + g * a.vdim + c);
-                Vt[(c + 0) * VS + key] = __float2bfloat16_rn(v.x);
-                Vt[(c + 1) * VS + key] = __float2bfloat16_rn(v.y);
-                Vt[(c + 2) * VS + key] = __float2bfloat16_rn(v.z);
-                Vt[(c + 3) * VS + key] = __float2bfloat16_rn(v.w);
+            // V transposed: neighbouring lanes take neighbouring keys of the same 4 channels, so the 2-byte stores of a warp fall into
+            // neighbouring words of a channel's row (the row-major reads of a key are spread over rounds and come out of L1)
+            {
+                constexpr int VN4 = AT_K * (DV / 4) / 128;
+#pragma unroll
+                for (int b0 = 0; b0 < VN4; b0 += 8) {
+                    float4 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int i = threadIdx.x + (b0 + u) * 128, key = i % AT_K, c = (i / AT_K) * 4;
+                        v[u] = (key < nk && c < a.vdim) ? *reinterpret_cast<const float4*>(vc + (size_t)(j0 + key) * ldv + g * a.vdim + c)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int i = threadIdx.x + (b0 + u) * 128, key = i % AT_K, c = (i / AT_K) * 4;
+                        Vt[(c + 0) * VS + key] = __float2bfloat16_rn(v[u].x);
+                        Vt[(c + 1) * VS + key] = __float2bfloat16_rn(v[u].y);
+                        Vt[(c + 2) * VS + key] = __float2bfloat16_rn(v[u].z);
+                        Vt[(c + 3) * VS + key] = __float2bfloat16_rn(v[u].w);
+                    }
+                }
             }
             __syncthreads();
             // scores of 16 queries x 64 keys
