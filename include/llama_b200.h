@@ -260,11 +260,30 @@ B200_API const char* b200_batch_last_error(b200_batch* batch);   /* message of t
  *   B200_MIX_GATED_DELTA    gated delta rule: causal depthwise convolutions (conv taps) + SiLU on q, k, v, unit-length q and k
  *          (q also times dim^-1/2), per-head write strength sigmoid(.) and decay exp(-exp(A_log) * softplus(. + dt_bias)),
  *          S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q;  per-head RMS norm with a shared weight, SiLU gate.
- * Feed-forward: none (ff = 0) or W_down act(W_up h) with act = relu(z)^2.
+ *   B200_MIX_SOFTMAX_ATTN   softmax attention with its parts as options (b200_softmax_attn_desc): grouped K/V heads, separate q/k and
+ *          v head sizes; optional biases of the q/k/v projections; optional causal depthwise convolution (conv taps, no activation)
+ *          directly after the projection, whose last conv - 1 inputs per sequence are state; q/k norm per head with a weight, over the
+ *          whole projection with a weight, or per head without one; optional rotary positions on the first rot_dims channels of a
+ *          head (channel 2i paired with 2i + 1, angle = position * rot_base^(-2i / rot_dims)), applied before the norm; score * scale,
+ *          then optionally softcap * tanh(score / softcap) and / or minus 2^(-dist_bias_exp (h + 1) / heads) * (i - j) for head h;
+ *          mask: sliding window (0 <= i - j < mask_size) or chunks counted from position 0 (j <= i, floor(i / mask_size) =
+ *          floor(j / mask_size)); value blending across layers: the first layer with v_mix = B200_VMIX_SOURCE publishes its values
+ *          of the step's tokens, a layer with B200_VMIX_BLEND caches (1 - l) v + l v_source, l = its scalar '.vmix'; output gate
+ *          per channel or one sigmoid per head.
+ * Feed-forward (ff_kind): B200_FF_RELU2 W_down relu(W_up h)^2 of width ff (none when ff = 0); B200_FF_GATED_GELU W_down (gelu_tanh(W_gate h)
+ * * W_up h) of width ff; B200_FF_MOE: router logits W_router h in f32, the `top` largest are chosen and weighted by the softmax over
+ * the chosen logits, experts W_down relu(W_up h)^2 of width expert_ff, plus an always-on expert of width shared_ff (0 = none).
+ * Layer form (program): post_norm = 0: x += sublayer(norm(x)); post_norm = 1: x <- norm(residual_alpha * x + sublayer(x)), the
+ * sublayers read x itself.  Norm weights are applied as (norm_weight_offset + w).
  * Embedding: row * embed_scale (+ sinusoidal position vector, pos_sinusoid); logits = head . norm(x) * logit_scale.
  * compute: 0 = bf16 weights and GEMM operands with f32 accumulation (residual stream, norms, softmax, gates and every recurrent
  * state stay f32), 1 = everything in f32 (FMA, no reduced-precision matrix mode). */
-enum { B200_MIX_WINDOW_MEMORY = 1, B200_MIX_GATED_DELTA = 2 };
+enum { B200_MIX_WINDOW_MEMORY = 1, B200_MIX_GATED_DELTA = 2, B200_MIX_SOFTMAX_ATTN = 3 };
+enum { B200_MASK_WINDOW = 0, B200_MASK_CHUNK = 1 };
+enum { B200_QKNORM_NONE = 0, B200_QKNORM_HEAD_WEIGHT = 1, B200_QKNORM_WHOLE_WEIGHT = 2, B200_QKNORM_HEAD_UNIT = 3 };
+enum { B200_GATE_NONE = 0, B200_GATE_CHANNEL = 1, B200_GATE_HEAD = 2 };
+enum { B200_VMIX_NONE = 0, B200_VMIX_SOURCE = 1, B200_VMIX_BLEND = 2 };
+enum { B200_FF_RELU2 = 0, B200_FF_GATED_GELU = 1, B200_FF_MOE = 2 };
 enum { B200_COMPUTE_BF16 = 0, B200_COMPUTE_F32 = 1 };
 enum { B200_TYPE_BF16 = 30 };   /* ggml's id; accepted by layer-program contexts only */
 typedef struct b200_window_attn_desc {
@@ -280,13 +299,32 @@ typedef struct b200_matrix_memory_desc {
 typedef struct b200_gated_delta_desc {
     int32_t heads, kv_heads, dim, vdim, conv;
 } b200_gated_delta_desc;
+typedef struct b200_softmax_attn_desc {
+    int32_t heads, kv_heads, dim, vdim;
+    int32_t mask, mask_size;         /* B200_MASK_* */
+    float scale;
+    int32_t qkv_bias;                /* 1 = '<q|k|v>.b' are added in the projection */
+    int32_t conv;                    /* taps of the causal convolution on q, k, v ('<q|k|v>.conv', [channels, taps]); 0 = none */
+    int32_t qk_norm;                 /* B200_QKNORM_* ('.q.norm' / '.k.norm' of size dim, or of the whole projection) */
+    int32_t rot_dims;                /* 0 = no rotation */
+    float rot_base;
+    float softcap;                   /* 0 = none */
+    float dist_bias_exp;             /* 0 = none */
+    int32_t v_mix, out_gate;         /* B200_VMIX_*, B200_GATE_* ('.g': [heads * vdim, width] or [heads, width]) */
+} b200_softmax_attn_desc;
+typedef struct b200_moe_desc {
+    int32_t experts, top, expert_ff, shared_ff;
+} b200_moe_desc;
 typedef struct b200_layer_desc {
     int32_t mixer;                   /* B200_MIX_* */
     b200_window_attn_desc attn;      /* WINDOW_MEMORY */
     b200_matrix_memory_desc mem;     /* WINDOW_MEMORY */
     float attn_scale, mem_scale;     /* WINDOW_MEMORY: weights of the two branches in the sum */
     b200_gated_delta_desc delta;     /* GATED_DELTA */
-    int32_t ff;                      /* feed-forward width, 0 = the layer has no second sublayer */
+    int32_t ff;                      /* feed-forward width, 0 = the layer has no second sublayer (B200_FF_MOE: unused) */
+    b200_softmax_attn_desc sattn;    /* SOFTMAX_ATTN */
+    int32_t ff_kind;                 /* B200_FF_* */
+    b200_moe_desc moe;               /* B200_FF_MOE */
 } b200_layer_desc;
 typedef struct b200_program_desc {
     int32_t width, vocab, n_layers;
@@ -295,6 +333,9 @@ typedef struct b200_program_desc {
     int32_t pos_sinusoid;                       /* 1 = add the sinusoidal position vector to the embedding */
     int32_t loop_start, loop_stop, loop_times;  /* layers [start, stop) run `times` times in a row; a step vector per pass */
     int32_t compute;                            /* B200_COMPUTE_* */
+    int32_t post_norm;                          /* 1 = norm after the residual sum (see "Layer form") */
+    float residual_alpha;                       /* post_norm: weight of x in the sum */
+    float norm_weight_offset;                   /* norm weights are stored minus this (0 or 1) */
 } b200_program_desc;
 B200_API int b200_ctx_create_layers(const b200_program_desc* prog, const b200_layer_desc* layers, int device, b200_ctx** out);
 /* One batch of token runs: run i continues sequence slot seqs[i] with lens[i] tokens (concatenated in `tokens`).  want_rows are

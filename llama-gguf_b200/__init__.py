@@ -105,10 +105,24 @@ class GatedDeltaDesc(C.Structure):
     _fields_ = [("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("conv", C.c_int32)]
 
 
+class SoftmaxAttnDesc(C.Structure):
+    """b200_softmax_attn_desc"""
+    _fields_ = [("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("mask", C.c_int32),
+                ("mask_size", C.c_int32), ("scale", C.c_float), ("qkv_bias", C.c_int32), ("conv", C.c_int32), ("qk_norm", C.c_int32),
+                ("rot_dims", C.c_int32), ("rot_base", C.c_float), ("softcap", C.c_float), ("dist_bias_exp", C.c_float),
+                ("v_mix", C.c_int32), ("out_gate", C.c_int32)]
+
+
+class MoeDesc(C.Structure):
+    """b200_moe_desc"""
+    _fields_ = [("experts", C.c_int32), ("top", C.c_int32), ("expert_ff", C.c_int32), ("shared_ff", C.c_int32)]
+
+
 class LayerDesc(C.Structure):
     """b200_layer_desc"""
     _fields_ = [("mixer", C.c_int32), ("attn", WindowAttnDesc), ("mem", MatrixMemoryDesc), ("attn_scale", C.c_float),
-                ("mem_scale", C.c_float), ("delta", GatedDeltaDesc), ("ff", C.c_int32)]
+                ("mem_scale", C.c_float), ("delta", GatedDeltaDesc), ("ff", C.c_int32), ("sattn", SoftmaxAttnDesc),
+                ("ff_kind", C.c_int32), ("moe", MoeDesc)]
 
 
 class ProgramDesc(C.Structure):
@@ -116,10 +130,15 @@ class ProgramDesc(C.Structure):
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("max_seq_len", C.c_int32),
                 ("max_batch", C.c_int32), ("norm_eps", C.c_float), ("embed_scale", C.c_float), ("logit_scale", C.c_float),
                 ("pos_sinusoid", C.c_int32), ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32),
-                ("compute", C.c_int32)]
+                ("compute", C.c_int32), ("post_norm", C.c_int32), ("residual_alpha", C.c_float), ("norm_weight_offset", C.c_float)]
 
 
-MIX_WINDOW_MEMORY, MIX_GATED_DELTA = 1, 2
+MIX_WINDOW_MEMORY, MIX_GATED_DELTA, MIX_SOFTMAX_ATTN = 1, 2, 3
+MASK_WINDOW, MASK_CHUNK = 0, 1
+QKNORM_NONE, QKNORM_HEAD_WEIGHT, QKNORM_WHOLE_WEIGHT, QKNORM_HEAD_UNIT = 0, 1, 2, 3
+GATE_NONE, GATE_CHANNEL, GATE_HEAD = 0, 1, 2
+VMIX_NONE, VMIX_SOURCE, VMIX_BLEND = 0, 1, 2
+FF_RELU2, FF_GATED_GELU, FF_MOE = 0, 1, 2
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
 BF16 = 30   # ggml's id; layer-program contexts only
 

@@ -479,7 +479,23 @@ struct AttnGeom {
     float out_scale;                  // weight of the branch in the mixer's sum, applied before the rounding to the compute type
     int fused_prep;                   // the attention kernel norms q / k and writes the row's K, V itself (decoding: no prep launch)
     int cap;                          // positions a slot's cache holds
+    // options of the general softmax mixer (all off for the window-and-memory mixer)
+    int chunk;                        // 1: the mask is chunks of `window` positions counted from position 0 instead of a sliding window
+    float softcap;                    // > 0: score <- softcap tanh(score / softcap)
+    float slope_exp;                  // > 0: score -= 2^(-slope_exp (h + 1) / H) (i - j)
 };
+// out_gate: 0 none, 1 = sigmoid of a gate column per value channel, 2 = one gate column per head
+__device__ __forceinline__ float attn_gate(const AttnGeom& a, const float* gate_row, int h, int ch) {
+    return a.out_gate == 1 ? sigmoid_f(gate_row[h * a.vdim + ch]) : a.out_gate == 2 ? sigmoid_f(gate_row[h]) : 1.0f;
+}
+// first visible key of position i outside the kept first tokens
+__device__ __forceinline__ int attn_lo(const AttnGeom& a, int i) { return a.chunk ? (i / a.window) * a.window : max(0, i - a.window + 1); }
+__device__ __forceinline__ float attn_slope(const AttnGeom& a, int h) { return a.slope_exp > 0.0f ? exp2f(-a.slope_exp * (float)(h + 1) / (float)a.H) : 0.0f; }
+// what happens to a scaled score before the softmax
+__device__ __forceinline__ float attn_score(const AttnGeom& a, float s, float slope, int i, int j) {
+    if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
+    return s - slope * (float)(i - j);
+}
 __global__ void lp_attn_prep_kernel(StepMeta sm, AttnGeom a, const float* __restrict__ P, int ldp, const float* __restrict__ qw,
                                     const float* __restrict__ kw, float* __restrict__ qbuf) {
     const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -552,9 +568,10 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
         for (int d = threadIdx.x; d < a.dim; d += blockDim.x) qs[d] = q[d];
     }
     __syncthreads();
-    const int lo = max(0, i - a.window + 1);
+    const int lo = attn_lo(a, i);
     const int a_end = min(a.keep_first, lo);
     const int nb0 = (a_end + 31) >> 5, nb1 = (i + 1 - lo + 31) >> 5;
+    const float slope = attn_slope(a, h);
     float m = -INFINITY, l = 0.0f;
     float acc[VCH];
 #pragma unroll
@@ -606,6 +623,7 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
             for (int d = 0; d < a.dim; d++) d0 = fmaf(qs[d], kr[d], d0);
             s = d0 * a.scale;
         }
+        if (j < end) s = attn_score(a, s, slope, i, j);
         const float m_new = fmaxf(m, wmax(s));
         const float p = j < end ? expf(s - m_new) : 0.0f;
         const float corr = expf(m - m_new);      // (m = -inf on the warp's first block: 0)
@@ -656,13 +674,13 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
         lsum = fmaf(ml_s[2 * w + 1], wgt[w], lsum);
     }
     const float invl = 1.0f / lsum;
-    const float* gate = P + (size_t)r * ldp + a.g_off + h * a.vdim;
+    const float* gate = P + (size_t)r * ldp + a.g_off;
     for (int ch = threadIdx.x; ch < a.vdim; ch += blockDim.x) {
         float o = 0.0f;
 #pragma unroll
         for (int w = 0; w < ATT_WARPS; w++) o = fmaf(acc_s[w * a.vdim + ch], wgt[w], o);
         o *= invl;
-        if (a.out_gate) o *= sigmoid_f(gate[ch]);
+        o *= attn_gate(a, gate, h, ch);
         out[(size_t)r * a.out_ld + h * a.vdim + ch] = from_f<OutT>(o * a.out_scale);
     }
 }
@@ -719,8 +737,9 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
     for (int n = 0; n < DV / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
     const int first = p0 + t0, last = p0 + min(t0 + AT_Q, len) - 1;
-    const int lo0 = max(0, first - a.window + 1);
+    const int lo0 = attn_lo(a, first);
     const int a_end = min(a.keep_first, lo0);
+    const float slope = attn_slope(a, h);
     for (int part = 0; part < 2; part++) {
         const int beg = part ? lo0 : 0, end = part ? last + 1 : a_end;
         for (int j0 = beg; j0 < end; j0 += AT_K) {
@@ -795,8 +814,9 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
                 for (int e = 0; e < 4; e++) {
                     const int key = n * 8 + 2 * tig + (e & 1), j = j0 + key;
                     const int i = (e & 2) ? i1 : i0;
-                    const bool vis = key < nk && ((e & 2) ? ok1 : ok0) && j <= i && (i - j < a.window || j < a.keep_first);
-                    sc[n][e] = vis ? sc[n][e] * a.scale : -INFINITY;
+                    const bool vis = key < nk && ((e & 2) ? ok1 : ok0) && j <= i &&
+                                     (a.chunk ? i / a.window == j / a.window : (i - j < a.window || j < a.keep_first));
+                    sc[n][e] = vis ? attn_score(a, sc[n][e] * a.scale, slope, i, j) : -INFINITY;
                 }
                 mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
                 mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
@@ -845,8 +865,8 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
         }
     }
     const float inv0 = ok0 ? a.out_scale / l0 : 0.0f, inv1 = ok1 ? a.out_scale / l1 : 0.0f;
-    const float* gate0 = P + (size_t)(r0 + tq0) * ldp + a.g_off + h * a.vdim;
-    const float* gate1 = P + (size_t)(r0 + tq1) * ldp + a.g_off + h * a.vdim;
+    const float* gate0 = P + (size_t)(r0 + tq0) * ldp + a.g_off;
+    const float* gate1 = P + (size_t)(r0 + tq1) * ldp + a.g_off;
     bf16* out0 = out + (size_t)(r0 + tq0) * a.out_ld + h * a.vdim;
     bf16* out1 = out + (size_t)(r0 + tq1) * a.out_ld + h * a.vdim;
 #pragma unroll
@@ -854,11 +874,11 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
         const int ch = n * 8 + 2 * tig;
         if (ch < a.vdim) {
             if (ok0) {
-                const float g0 = a.out_gate ? sigmoid_f(gate0[ch]) : 1.0f, g1 = a.out_gate ? sigmoid_f(gate0[ch + 1]) : 1.0f;
+                const float g0 = attn_gate(a, gate0, h, ch), g1 = attn_gate(a, gate0, h, ch + 1);
                 *reinterpret_cast<uint32_t*>(out0 + ch) = pack_bf2(o[n][0] * inv0 * g0, o[n][1] * inv0 * g1);
             }
             if (ok1) {
-                const float g0 = a.out_gate ? sigmoid_f(gate1[ch]) : 1.0f, g1 = a.out_gate ? sigmoid_f(gate1[ch + 1]) : 1.0f;
+                const float g0 = attn_gate(a, gate1, h, ch), g1 = attn_gate(a, gate1, h, ch + 1);
                 *reinterpret_cast<uint32_t*>(out1 + ch) = pack_bf2(o[n][2] * inv1 * g0, o[n][3] * inv1 * g1);
             }
         }
@@ -1180,6 +1200,14 @@ __global__ void lp_argmax_kernel(const float* __restrict__ logits, int vocab, in
     if (threadIdx.x == 0) out[blockIdx.x] = si[0];
 }
 
+#include "lp_softmax_attn.cuh"
+#include "lp_ffn.cuh"
+
+__global__ void lp_add_scalar_kernel(float* __restrict__ v, int n, float a) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) v[i] += a;
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 struct Tensor {
     void* d = nullptr;      // matrices: compute type; vectors: f32
@@ -1201,6 +1229,13 @@ struct LayerPlan {
     void *wo_cat = nullptr, *wo_delta = nullptr, *w_up = nullptr, *w_down = nullptr;   // wo_cat: [width][attention | memory]
     int k_cat = 0;
     size_t kv_bytes = 0, rec_bytes = 0;   // per run, per slot (kv_bytes for `cap` positions)
+    // general softmax mixer
+    PrepGeom pg{};
+    const float *qkv_bias = nullptr, *vmix = nullptr;
+    const double* rot_freq = nullptr;
+    void* wo = nullptr;
+    // feed-forward: n_up rows of w_up ([up] | [gate | up] | [router | experts' up | always-on expert's up]), k_down columns of w_down
+    int n_up = 0, k_down = 0;
 };
 
 struct SlotMem {
@@ -1231,6 +1266,9 @@ struct LpModel {
     uint8_t* d_meta = nullptr;
     size_t meta_bytes = 0;
     float *x = nullptr, *P = nullptr, *qbuf = nullptr, *O = nullptr, *conv = nullptr, *logits = nullptr;
+    float *y = nullptr, *vsrc = nullptr, *moe_w = nullptr, *moe_selw = nullptr;   // sublayer output (norm-after-sum layers), shared values, routing
+    int* moe_sel = nullptr;
+    int max_vsrc = 0, max_experts = 0, max_top = 0;
     void *hn = nullptr, *act_a = nullptr, *hw = nullptr;
     int* pick = nullptr;
     float* h_logits = nullptr;          // pinned
@@ -1311,7 +1349,7 @@ bool is_matrix_name(const std::string& n) {
     // everything a GEMM or the embedding gather reads; the rest (norm weights, biases, convolution taps, per-head constants, step
     // vectors) is kept in f32
     if (n == "embed" || n == "head") return true;
-    static const char* suf[] = {".q", ".k", ".v", ".g", ".o", ".i", ".f", ".a", ".b", ".up", ".down"};
+    static const char* suf[] = {".q", ".k", ".v", ".g", ".o", ".i", ".f", ".a", ".b", ".up", ".down", ".gate", ".router"};
     for (const char* s : suf) {
         const size_t L = strlen(s);
         if (n.size() > L && n.compare(n.size() - L, L, s) == 0) return true;
@@ -1475,7 +1513,30 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
             const b200_gated_delta_desc& g = L.delta;
             if (g.heads <= 0 || g.kv_heads <= 0 || g.dim <= 0 || g.vdim <= 0 || g.kv_heads > g.heads || g.conv < 1) return bad(at + "bad delta-rule sizes");
             if (g.dim > 256) return bad(at + "delta-rule key size above 256");
+        } else if (L.mixer == B200_MIX_SOFTMAX_ATTN) {
+            const b200_softmax_attn_desc& a = L.sattn;
+            if (a.heads <= 0 || a.kv_heads <= 0 || a.dim <= 0 || a.vdim <= 0 || a.kv_heads > a.heads || a.heads % a.kv_heads)
+                return bad(at + "bad attention head counts or sizes");
+            if (a.mask_size <= 0 || (a.mask != B200_MASK_WINDOW && a.mask != B200_MASK_CHUNK)) return bad(at + "bad attention mask");
+            if (a.vdim > 32 * ATT_ACC) return bad(at + "attention value size above " + std::to_string(32 * ATT_ACC));
+            if (a.rot_dims < 0 || a.rot_dims > a.dim || (a.rot_dims & 1) || (a.rot_dims > 0 && !(a.rot_base > 0.0f))) return bad(at + "bad rotary sizes");
+            if (a.qk_norm < B200_QKNORM_NONE || a.qk_norm > B200_QKNORM_HEAD_UNIT) return bad(at + "unknown q/k norm");
+            if (a.out_gate < B200_GATE_NONE || a.out_gate > B200_GATE_HEAD) return bad(at + "unknown output gate");
+            if (a.v_mix < B200_VMIX_NONE || a.v_mix > B200_VMIX_BLEND) return bad(at + "unknown value mixing");
+            if (a.conv < 0 || a.softcap < 0.0f || a.dist_bias_exp < 0.0f) return bad(at + "negative attention constant");
+            if (a.v_mix == B200_VMIX_BLEND) {
+                int src = -1;
+                for (int j = 0; j < i; j++)
+                    if (layers[j].mixer == B200_MIX_SOFTMAX_ATTN && layers[j].sattn.v_mix == B200_VMIX_SOURCE) src = j;
+                if (src < 0) return bad(at + "values are blended but no earlier layer is their source");
+                if (layers[src].sattn.kv_heads * layers[src].sattn.vdim != a.kv_heads * a.vdim) return bad(at + "blended values differ in size from their source");
+            }
+            if (looped && a.v_mix != B200_VMIX_NONE) return bad(at + "value mixing inside a program with a repeated range is not supported");
         } else return bad(at + "unknown mixer");
+        if (L.ff_kind == B200_FF_MOE) {
+            const b200_moe_desc& e = L.moe;
+            if (e.experts <= 0 || e.top <= 0 || e.top > e.experts || e.expert_ff <= 0 || e.shared_ff < 0) return bad(at + "bad mixture-of-experts sizes");
+        } else if (L.ff_kind != B200_FF_RELU2 && L.ff_kind != B200_FF_GATED_GELU) return bad(at + "unknown feed-forward kind");
         if (L.ff < 0) return bad(at + "negative feed-forward width");
     }
     LpModel* m = new LpModel();
@@ -1678,6 +1739,64 @@ int lp_finalize(LpModel* m, std::string* err) {
             m->max_act = std::max(m->max_act, L.k_cat);
             m->max_o = std::max(m->max_o, mm.heads * mm.vdim);
             m->max_q = std::max(m->max_q, a.heads * a.dim);
+        } else if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) {
+            const b200_softmax_attn_desc& a = L.d.sattn;
+            const std::string x = pre + "mix.";
+            const uint64_t nq = (uint64_t)a.heads * a.dim, nk = (uint64_t)a.kv_heads * a.dim, nv = (uint64_t)a.kv_heads * a.vdim;
+            std::vector<std::string> names = {x + "q", x + "k", x + "v"};
+            std::vector<uint64_t> rows = {nq, nk, nv};
+            if (a.out_gate) { names.push_back(x + "g"); rows.push_back(a.out_gate == B200_GATE_HEAD ? (uint64_t)a.heads : (uint64_t)a.heads * a.vdim); }
+            if ((rc = fuse_rows(m, names, rows, W, &L.w_in, &L.n_in, &off, err))) return rc;
+            AttnGeom& g = L.ag;
+            g.H = a.heads; g.G = a.kv_heads; g.dim = a.dim; g.vdim = a.vdim; g.window = a.mask_size; g.keep_first = 0;
+            g.chunk = a.mask == B200_MASK_CHUNK ? 1 : 0; g.softcap = a.softcap; g.slope_exp = a.dist_bias_exp;
+            g.qk_norm = 0; g.out_gate = a.out_gate; g.scale = a.scale; g.eps = p.norm_eps; g.cap = p.max_seq_len;
+            g.q_off = off[0]; g.k_off = off[1]; g.v_off = off[2]; g.g_off = a.out_gate ? off[3] : 0;
+            PrepGeom& q = L.pg;
+            q.C = (int)(nq + nk + nv); q.taps = a.conv; q.qk_norm = a.qk_norm; q.rot_dims = a.rot_dims; q.v_mix = a.v_mix;
+            // concatenate per-part vectors ([q | k | v] order of the projection) into one device table; `per` values per channel
+            auto cat3 = [&](const char* suffix, uint64_t per, const float** out) -> int {
+                const float* part[3];
+                const uint64_t n[3] = {nq * per, nk * per, nv * per};
+                const char* nm[3] = {"q", "k", "v"};
+                for (int i = 0; i < 3; i++)
+                    if ((rc = need_vec(m, x + nm[i] + suffix, n[i], &part[i], err))) return rc;
+                float* d = nullptr;
+                LCU_ALLOC(cudaMalloc((void**)&d, up16((n[0] + n[1] + n[2]) * 4)));
+                LCU(cudaMemcpy(d, part[0], n[0] * 4, cudaMemcpyDeviceToDevice));
+                LCU(cudaMemcpy(d + n[0], part[1], n[1] * 4, cudaMemcpyDeviceToDevice));
+                LCU(cudaMemcpy(d + n[0] + n[1], part[2], n[2] * 4, cudaMemcpyDeviceToDevice));
+                Tensor t;
+                t.d = d; t.rows = q.C; t.cols = per; t.bytes = (n[0] + n[1] + n[2]) * 4;
+                m->tensors[x + "qkv" + suffix] = t;
+                *out = d;
+                return B200_OK;
+            };
+            if (a.qkv_bias && (rc = cat3(".b", 1, &L.qkv_bias))) return rc;
+            if (q.taps > 0 && (rc = cat3(".conv", q.taps, &L.conv_w))) return rc;
+            if (a.qk_norm == B200_QKNORM_HEAD_WEIGHT || a.qk_norm == B200_QKNORM_WHOLE_WEIGHT) {
+                const bool whole = a.qk_norm == B200_QKNORM_WHOLE_WEIGHT;
+                if ((rc = need_vec(m, x + "q.norm", whole ? nq : (uint64_t)a.dim, &L.qn, err))) return rc;
+                if ((rc = need_vec(m, x + "k.norm", whole ? nk : (uint64_t)a.dim, &L.kn, err))) return rc;
+            }
+            if (a.rot_dims > 0) {   // f_i = base^(-2i / dims), in double
+                std::vector<double> f(a.rot_dims / 2);
+                for (int i = 0; i < a.rot_dims / 2; i++) f[i] = std::pow((double)a.rot_base, -2.0 * (double)i / (double)a.rot_dims);
+                double* d = nullptr;
+                LCU_ALLOC(cudaMalloc((void**)&d, up16(f.size() * 8)));
+                LCU(cudaMemcpy(d, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
+                Tensor t;
+                t.d = d; t.rows = 1; t.cols = f.size(); t.bytes = f.size() * 8;
+                m->tensors[x + "rot.freq"] = t;
+                L.rot_freq = d;
+            }
+            if (a.v_mix == B200_VMIX_BLEND && (rc = need_vec(m, x + "vmix", 1, &L.vmix, err))) return rc;
+            if ((rc = need_mat(m, x + "o", W, (uint64_t)a.heads * a.vdim, &L.wo, err))) return rc;
+            L.kv_bytes = up16((size_t)p.max_seq_len * (nk + nv) * 4);
+            L.rec_bytes = q.taps > 1 ? up16((size_t)(q.taps - 1) * q.C * 4) : 0;
+            m->max_act = std::max(m->max_act, a.heads * a.vdim);
+            m->max_q = std::max(m->max_q, (int)nq);
+            if (a.v_mix != B200_VMIX_NONE) m->max_vsrc = std::max(m->max_vsrc, (int)nv);
         } else {
             const b200_gated_delta_desc& g = L.d.delta;
             const std::string x = pre + "mix.";
@@ -1712,12 +1831,76 @@ int lp_finalize(LpModel* m, std::string* err) {
             m->max_conv = std::max(m->max_conv, d.C);
         }
         m->max_in = std::max(m->max_in, L.n_in);
-        if (L.d.ff > 0) {
+        if (L.d.ff_kind == B200_FF_MOE) {
+            const b200_moe_desc& e = L.d.moe;
             if ((rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
-            if ((rc = need_mat(m, pre + "mlp.up", L.d.ff, W, &L.w_up, err))) return rc;
+            std::vector<std::string> names = {pre + "mlp.router"}, down;
+            std::vector<uint64_t> rows = {(uint64_t)e.experts};
+            for (int i = 0; i < e.experts; i++) {
+                names.push_back(pre + "mlp.e" + std::to_string(i) + ".up");
+                rows.push_back(e.expert_ff);
+                down.push_back(pre + "mlp.e" + std::to_string(i) + ".down");
+            }
+            if (e.shared_ff > 0) {
+                names.push_back(pre + "mlp.shared.up");
+                rows.push_back(e.shared_ff);
+                down.push_back(pre + "mlp.shared.down");
+            }
+            std::vector<int> uoff;
+            if ((rc = fuse_rows(m, names, rows, W, &L.w_up, &L.n_up, &uoff, err))) return rc;
+            {
+                Tensor t;
+                t.d = L.w_up; t.matrix = true; t.rows = L.n_up; t.cols = W; t.bytes = (size_t)L.n_up * W * elt(m);
+                m->tensors[pre + "mlp.up_cat"] = t;
+            }
+            // the down projections side by side: [width][e0 | e1 | ... | always-on]: one product with the weighted activations
+            L.k_down = e.experts * e.expert_ff + e.shared_ff;
+            const size_t es = elt(m);
+            LCU_ALLOC(cudaMalloc(&L.w_down, up16(W * (size_t)L.k_down * es)));
+            for (size_t i = 0; i < down.size(); i++) {
+                const size_t k = i < (size_t)e.experts ? e.expert_ff : e.shared_ff;
+                void* src;
+                if ((rc = need_mat(m, down[i], W, k, &src, err))) return rc;
+                LCU(cudaMemcpy2D((uint8_t*)L.w_down + i * e.expert_ff * es, (size_t)L.k_down * es, src, k * es, k * es, W, cudaMemcpyDeviceToDevice));
+                cudaFree(m->tensors[down[i]].d);
+                m->tensors.erase(down[i]);
+            }
+            Tensor t;
+            t.d = L.w_down; t.matrix = true; t.rows = W; t.cols = L.k_down; t.bytes = W * (size_t)L.k_down * es;
+            m->tensors[pre + "mlp.down_cat"] = t;
+            m->max_act = std::max(m->max_act, L.k_down);
+            m->max_in = std::max(m->max_in, L.n_up);
+            m->max_experts = std::max(m->max_experts, e.experts);
+            m->max_top = std::max(m->max_top, e.top);
+        } else if (L.d.ff > 0) {
+            if ((rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
+            if (L.d.ff_kind == B200_FF_GATED_GELU) {
+                std::vector<int> uoff;
+                if ((rc = fuse_rows(m, {pre + "mlp.gate", pre + "mlp.up"}, {(uint64_t)L.d.ff, (uint64_t)L.d.ff}, W, &L.w_up, &L.n_up, &uoff, err))) return rc;
+                Tensor t;
+                t.d = L.w_up; t.matrix = true; t.rows = L.n_up; t.cols = W; t.bytes = (size_t)L.n_up * W * elt(m);
+                m->tensors[pre + "mlp.gate_up"] = t;
+                m->max_in = std::max(m->max_in, L.n_up);
+            } else {
+                if ((rc = need_mat(m, pre + "mlp.up", L.d.ff, W, &L.w_up, err))) return rc;
+                L.n_up = L.d.ff;
+            }
             if ((rc = need_mat(m, pre + "mlp.down", W, L.d.ff, &L.w_down, err))) return rc;
+            L.k_down = L.d.ff;
             m->max_act = std::max(m->max_act, L.d.ff);
+        } else if (p.post_norm && find(m, pre + "norm2")) {   // a layer without feed-forward whose file still holds the second norm
+            if ((rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
         }
+    }
+    if (p.norm_weight_offset != 0.0f) {   // norm weights stored around zero: (offset + w) once, in f32
+        std::vector<std::string> nm = {"final.norm"};
+        for (int li = 0; li < p.n_layers; li++)
+            for (const char* s2 : {".norm1", ".norm2"}) nm.push_back("l" + std::to_string(li) + s2);
+        for (const std::string& n : nm) {
+            const Tensor* t = find(m, n);
+            if (t) lp_add_scalar_kernel<<<(unsigned)((t->rows * t->cols + 255) / 256), 256>>>((float*)t->d, (int)(t->rows * t->cols), p.norm_weight_offset);
+        }
+        LCU(cudaDeviceSynchronize());
     }
     // layout of a slot: cache block (all runs with attention) and state block (all runs)
     size_t kv = 0, rec = 0;
@@ -1729,6 +1912,7 @@ int lp_finalize(LpModel* m, std::string* err) {
         rec += L.rec_bytes;
         m->weight_bytes += 0;
         if (L.d.mixer == B200_MIX_WINDOW_MEMORY) m->kv_bytes_per_pos += (size_t)L.d.attn.kv_heads * (L.d.attn.dim + L.d.attn.vdim) * 4;
+        if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) m->kv_bytes_per_pos += (size_t)L.d.sattn.kv_heads * (L.d.sattn.dim + L.d.sattn.vdim) * 4;
     }
     m->slot_kv_bytes = std::max<size_t>(kv, 256);
     m->slot_rec_bytes = std::max<size_t>(rec, 256);
@@ -1762,7 +1946,8 @@ void lp_destroy(LpModel* m) {
     for (SlotMem& s : m->slot) { cudaFree(s.kv); cudaFree(s.rec); }
     for (SlotMem& s : m->pool) { cudaFree(s.kv); cudaFree(s.rec); }
     for (void* ptr : {(void*)m->inv_freq, (void*)m->d_meta, (void*)m->x, (void*)m->P, (void*)m->qbuf, (void*)m->O, (void*)m->conv, (void*)m->logits,
-                      m->hn, m->act_a, m->hw, (void*)m->pick, (void*)m->taps})
+                      m->hn, m->act_a, m->hw, (void*)m->pick, (void*)m->taps, (void*)m->y, (void*)m->vsrc, (void*)m->moe_w, (void*)m->moe_selw,
+                      (void*)m->moe_sel})
         cudaFree(ptr);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_logits) cudaFreeHost(m->h_logits);
@@ -1828,6 +2013,13 @@ int ensure_scratch(LpModel* m, int R, int n_runs, int n_want, std::string* err) 
         if ((rc = grow(&m->conv, (size_t)cap * std::max(m->max_conv, 1) * 4, err))) return rc;
         if ((rc = grow(&m->hn, (size_t)cap * W * es, err))) return rc;
         if ((rc = grow(&m->act_a, (size_t)cap * m->max_act * es, err))) return rc;
+        if (m->p.post_norm && (rc = grow(&m->y, (size_t)cap * W * 4, err))) return rc;
+        if (m->max_vsrc > 0 && (rc = grow(&m->vsrc, (size_t)cap * m->max_vsrc * 4, err))) return rc;
+        if (m->max_experts > 0) {
+            if ((rc = grow(&m->moe_w, (size_t)cap * m->max_experts * 4, err))) return rc;
+            if ((rc = grow(&m->moe_selw, (size_t)cap * m->max_top * 4, err))) return rc;
+            if ((rc = grow(&m->moe_sel, (size_t)cap * m->max_top * 4, err))) return rc;
+        }
         m->cap_rows = cap;
     }
     if (n_want > m->cap_want) {
@@ -1876,6 +2068,20 @@ bool attn_tile(LpModel* m, const StepMeta& sm, const AttnGeom& ag, int ldp, int 
     return attn_tile_launch<128, 256>(m, sm, ag, ldp, n_runs, max_len);
 }
 
+// The warp kernel: any row count, both compute modes.
+void attn_rows(LpModel* m, const StepMeta& sm, const AttnGeom& ag, const LayerPlan& L, int R) {
+    dim3 agrid(R, ag.H);
+    const size_t asmem = (size_t)(((ag.dim + 3) & ~3) + ATT_WARPS * ag.vdim + 2 * ATT_WARPS) * 4;
+    const int vch = ag.vdim <= 128 ? 4 : ag.vdim <= 256 ? 8 : 16;
+#define LP_ATTN(T, V) launch(m, lp_window_attn_kernel<T, V>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, L.qn, L.kn, (T*)m->act_a)
+    if (m->f32) {
+        if (vch == 4) LP_ATTN(float, 4); else if (vch == 8) LP_ATTN(float, 8); else LP_ATTN(float, 16);
+    } else {
+        if (vch == 4) LP_ATTN(bf16, 4); else if (vch == 8) LP_ATTN(bf16, 8); else LP_ATTN(bf16, 16);
+    }
+#undef LP_ATTN
+}
+
 // Every kernel of one step, in order, on the model's stream: eagerly, or while the stream is being captured into a CUDA graph (a
 // decode step: one row per run, nothing allocated).  head: 0 = no logits, 1 = logits of the wanted rows, 2 = their greedy picks.
 void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want, int head, int taps_len, int max_len) {
@@ -1885,30 +2091,51 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
     // embedding
     if (m->f32) launch(m, lp_embed_kernel<float>, dim3(R), dim3(128), 0, sm, (const float*)find(m, "embed")->d, m->inv_freq, m->x, W, p.embed_scale, p.pos_sinusoid);
     else launch(m, lp_embed_kernel<bf16>, dim3(R), dim3(128), 0, sm, (const bf16*)find(m, "embed")->d, m->inv_freq, m->x, W, p.embed_scale, p.pos_sinusoid);
+    // The two layer forms.  Norm first: a sublayer reads norm(x) and its output projection adds into x.  Norm after the sum
+    // (post_norm): a sublayer reads x itself -- m->hn holds x in the compute type -- its output projection goes to m->y, and
+    // lp_postnorm_kernel makes x <- norm(alpha x + y) and the next copy.
+    const bool post = p.post_norm != 0;
+    auto cast_x = [&](const float* y, const float* w) {
+        if (m->f32) launch(m, lp_postnorm_kernel<float>, dim3(R), dim3(256), 0, m->x, y, w, (float*)m->hn, W, p.residual_alpha, p.norm_eps);
+        else launch(m, lp_postnorm_kernel<bf16>, dim3(R), dim3(256), 0, m->x, y, w, (bf16*)m->hn, W, p.residual_alpha, p.norm_eps);
+    };
+    auto project_in = [&](const float* add, const float* nw, const void* Wm, int N, void* Y, int ldy, int epi) {
+        if (post) gemm(m, m->hn, W, Wm, N, W, Y, ldy, R, 1.0f, epi);
+        else norm_gemm(m, m->x, add, nullptr, nw, m->hn, Wm, N, Y, ldy, R, 1.0f, epi);
+    };
+    auto project_out = [&](const void* X, int K, const void* Wm, const float* nw) {
+        if (post) {
+            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE);
+            cast_x(m->y, nw);
+        } else gemm(m, X, K, Wm, W, K, m->x, W, R, 1.0f, EPI_ADD);
+    };
+    if (post) cast_x(nullptr, nullptr);
     for (size_t run = 0; run < m->runs.size(); run++) {
         LayerPlan& L = m->plan[m->runs[run]];
         const float* add = m->run_pass[run] >= 0 ? loop_step + (size_t)m->run_pass[run] * W : nullptr;
-        norm_gemm(m, m->x, add, nullptr, L.norm1, m->hn, L.w_in, L.n_in, m->P, L.n_in, R, 1.0f, EPI_STORE);
-        if (L.d.mixer == B200_MIX_WINDOW_MEMORY) {
+        project_in(add, L.norm1, L.w_in, L.n_in, m->P, L.n_in, EPI_STORE);
+        if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) {
+            AttnGeom ag = L.ag;
+            ag.kv_off = m->run_kv_off[run];
+            ag.out_ld = ag.H * ag.vdim;
+            ag.out_scale = 1.0f;
+            ag.fused_prep = 0;
+            PrepGeom pg = L.pg;
+            pg.rec_off = m->run_rec_off[run];
+            const size_t psmem = (size_t)(((pg.C + 3) & ~3) + pg.rot_dims) * 4;
+            launch(m, lp_attn_prep2_kernel, dim3(R), dim3(256), psmem, sm, ag, pg, (const float*)m->P, L.n_in, L.qkv_bias, L.conv_w, L.qn, L.kn, L.rot_freq,
+                   L.vmix, m->vsrc, m->qbuf);
+            if (pg.taps > 1) launch(m, lp_attn_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, pg, (const float*)m->P, L.n_in, L.qkv_bias);
+            if (!attn_tile(m, sm, ag, L.n_in, n_runs, max_len)) attn_rows(m, sm, ag, L, R);
+            project_out(m->act_a, ag.out_ld, L.wo, L.norm1);
+        } else if (L.d.mixer == B200_MIX_WINDOW_MEMORY) {
             AttnGeom ag = L.ag;
             ag.kv_off = m->run_kv_off[run];
             ag.out_ld = L.k_cat;
             ag.out_scale = L.d.attn_scale;
             ag.fused_prep = (m->use_fuse && max_len == 1) ? 1 : 0;
             if (!ag.fused_prep) launch(m, lp_attn_prep_kernel, dim3(R), dim3(128), 0, sm, ag, (const float*)m->P, L.n_in, L.qn, L.kn, m->qbuf);
-            if (attn_tile(m, sm, ag, L.n_in, n_runs, max_len)) {
-            } else {
-            dim3 agrid(R, ag.H);
-            const size_t asmem = (size_t)(((ag.dim + 3) & ~3) + ATT_WARPS * ag.vdim + 2 * ATT_WARPS) * 4;
-            const int vch = ag.vdim <= 128 ? 4 : ag.vdim <= 256 ? 8 : 16;
-#define LP_ATTN(T, V) launch(m, lp_window_attn_kernel<T, V>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, L.qn, L.kn, (T*)m->act_a)
-            if (m->f32) {
-                if (vch == 4) LP_ATTN(float, 4); else if (vch == 8) LP_ATTN(float, 8); else LP_ATTN(float, 16);
-            } else {
-                if (vch == 4) LP_ATTN(bf16, 4); else if (vch == 8) LP_ATTN(bf16, 8); else LP_ATTN(bf16, 16);
-            }
-#undef LP_ATTN
-            }
+            if (!attn_tile(m, sm, ag, L.n_in, n_runs, max_len)) attn_rows(m, sm, ag, L, R);
             MemGeom mg = L.mg;
             mg.rec_off = m->run_rec_off[run];
             const int ldo = mg.H * mg.vdim;
@@ -1923,7 +2150,7 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             dim3 hgrid(R, (mg.H + 3) / 4);
             if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (float*)m->act_a + ag.H * ag.vdim, L.k_cat, L.d.mem_scale, R);
             else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (bf16*)m->act_a + ag.H * ag.vdim, L.k_cat, L.d.mem_scale, R);
-            gemm(m, m->act_a, L.k_cat, L.wo_cat, W, L.k_cat, m->x, W, R, 1.0f, EPI_ADD);
+            project_out(m->act_a, L.k_cat, L.wo_cat, L.norm1);
         } else {
             DeltaGeom dg = L.dg;
             dg.rec_off = m->run_rec_off[run];
@@ -1942,11 +2169,29 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             dim3 hgrid(R, (dg.H + 3) / 4);
             if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (float*)m->act_a, ldo, 1.0f, R);
             else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (bf16*)m->act_a, ldo, 1.0f, R);
-            gemm(m, m->act_a, ldo, L.wo_delta, W, ldo, m->x, W, R, 1.0f, EPI_ADD);
+            project_out(m->act_a, ldo, L.wo_delta, L.norm1);
         }
-        if (L.d.ff > 0) {
-            norm_gemm(m, m->x, nullptr, nullptr, L.norm2, m->hn, L.w_up, L.d.ff, m->act_a, L.d.ff, R, 1.0f, EPI_RELU2);
-            gemm(m, m->act_a, L.d.ff, L.w_down, W, L.d.ff, m->x, W, R, 1.0f, EPI_ADD);
+        if (L.d.ff_kind == B200_FF_MOE) {
+            // one product for [router | every expert's up | the always-on expert's up] (f32 out), the router's choice per row, the
+            // activations times their expert's weight (0 for experts that were not chosen), one product with the down matrices side by side
+            const b200_moe_desc& e = L.d.moe;
+            project_in(nullptr, L.norm2, L.w_up, L.n_up, m->P, L.n_up, EPI_STORE);
+            launch(m, lp_moe_route_kernel, dim3((R + 3) / 4), dim3(128), 0, (const float*)m->P, L.n_up, e.experts, e.top, m->moe_w, m->moe_sel, m->moe_selw, R);
+            const unsigned nb = (unsigned)(((size_t)R * L.k_down + 255) / 256);
+            if (m->f32) launch(m, lp_moe_act_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, e.experts, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (float*)m->act_a, R);
+            else launch(m, lp_moe_act_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, e.experts, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (bf16*)m->act_a, R);
+            project_out(m->act_a, L.k_down, L.w_down, L.norm2);
+        } else if (L.d.ff > 0 && L.d.ff_kind == B200_FF_GATED_GELU) {
+            project_in(nullptr, L.norm2, L.w_up, L.n_up, m->P, L.n_up, EPI_STORE);
+            const unsigned nb = (unsigned)(((size_t)R * L.d.ff + 255) / 256);
+            if (m->f32) launch(m, lp_gated_gelu_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, (float*)m->act_a, L.d.ff, R);
+            else launch(m, lp_gated_gelu_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, (bf16*)m->act_a, L.d.ff, R);
+            project_out(m->act_a, L.d.ff, L.w_down, L.norm2);
+        } else if (L.d.ff > 0) {
+            project_in(nullptr, L.norm2, L.w_up, L.d.ff, m->act_a, L.d.ff, EPI_RELU2);
+            project_out(m->act_a, L.d.ff, L.w_down, L.norm2);
+        } else if (post && L.norm2) {
+            cast_x(nullptr, L.norm2);
         }
         if (taps_len > 0) cudaMemcpyAsync(m->taps + run * (size_t)taps_len * W, m->x, (size_t)taps_len * W * 4, cudaMemcpyDeviceToDevice, m->stream);
     }

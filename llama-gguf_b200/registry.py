@@ -14,7 +14,12 @@ def _lazilorn(path, **kw):
     return lazilorn.load(path, **kw)
 
 
-LOADERS = {"Lazilorn": _lazilorn}
+def _mefurax(path, **kw):
+    from . import mefurax
+    return mefurax.load(path, **kw)
+
+
+LOADERS = {"Lazilorn": _lazilorn, "Mefurax": _mefurax}
 
 
 def architecture_of(path):
