@@ -508,3 +508,40 @@ def test_tensor_core_gemm_path(b200, monkeypatch):
     ref = O.Model(cfg, w).forward(toks)
     d = np.array([S.rel_err(outs["1"][2][i], ref[i]) for i in range(300)])
     assert np.median(d) < BF16_TOL and (d < BF16_TOL).mean() > 0.9
+
+
+# ---------------------------------------------------------------------------------------------------- the command line
+def test_trace_runner_on_a_model_folder(b200, tmp_path):
+    # config.json + model.safetensors (bf16) on disk -> registry -> bin/trace_run: two requests start together with unequal prompts, are
+    # decoded together, the shorter one ends first; logits of the wanted rows come back in files
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from llama_gguf_b200.safetensors_io import bf16_bits, write_safetensors
+
+    cfg = full_cfg()
+    w = S.random_weights(cfg, 51)
+    d = tmp_path / "model"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(str(d / "model.safetensors"), {n: bf16_bits(a).reshape(a.shape) for n, a in w.items()})
+    a, b = tokens(19, cfg["vocab"], 52), tokens(7, cfg["vocab"], 53)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": a[:15], "want": [0, 14]}, {"id": "y", "tokens": b[:5], "want": [4]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": a[15:16], "want": []}, {"id": "y", "tokens": b[5:6], "want": [0]}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": a[16:17], "want": [0]}, {"id": "y", "tokens": b[6:7], "want": [0]}], "end": ["y"]},
+             {"step": 3, "entries": [{"id": "x", "tokens": a[17:19], "want": [1]}], "end": ["x"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(d), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "64"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [ln for ln in r.stdout.split("\n") if ln.startswith("done")] == ["done %d" % i for i in range(4)]
+    ref = O.Model(cfg, w)
+    wa, wb = ref.forward(a), ref.forward(b)
+    got = {i: np.fromfile(str(out / ("%d.f32" % i)), dtype="<f4").reshape(-1, cfg["vocab"]) for i in range(4)}
+    assert S.rel_err(got[0], np.stack([wa[0], wa[14], wb[4]])) < F32_TOL
+    assert S.rel_err(got[1], wb[5:6]) < F32_TOL
+    assert S.rel_err(got[2], np.stack([wa[16], wb[6]])) < F32_TOL
+    assert S.rel_err(got[3], wa[18:19]) < F32_TOL
