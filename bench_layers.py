@@ -1,6 +1,7 @@
-"""bench.py --design lazilorn: prefill and decode throughput of the Lazilorn layer program at sizes that resemble a real model's
+"""bench.py --design lazilorn | mefurax: prefill and decode throughput of a layer-program design at sizes that resemble a real model's
 layers (random weights), beside the library's closest existing model -- a llama-architecture transformer of the same width, depth
-and parameter count in Q8_0 blocks (the densest weight type its tensor-core prompt path takes).
+and parameter count in Q8_0 blocks (the densest weight type its tensor-core prompt path takes); Mefurax also beside Lazilorn at
+the same width and depth (the other bf16 layer program, whose attention and GEMM kernels it shares).
 
 Per size and model: prompt tokens/s for one prompt of --prefill-len tokens, decode tokens/s at batch 1 and at --batch sequences
 after prompts of --prompt-len tokens.  Every number is host wall clock around the library call (each call ends with a stream
@@ -34,11 +35,34 @@ def lazilorn_config(s, window=1024, keep_first=4):
             "logit_scale": 1.0, "loop": {"start": 0, "stop": 0, "times": 1}, "layers": layers}
 
 
-def lazilorn_feeder(cfg, seed):
+MEFURAX_SIZES = {
+    # name: width, layers (a = windowed mixer with convolution and distance bias, b = chunked rotary mixer; the first layer's feed-forward
+    # is dense, the others are mixtures), heads / kv heads, dense ff, experts / chosen / expert ff / always-on ff
+    "w1024": dict(width=1024, pattern="bbabba", heads=8, kv_heads=2, ff=4096, experts=8, top=2, eff=1024, sff=1024, vocab=32000),
+    "w2048": dict(width=2048, pattern="bbabbbab", heads=16, kv_heads=4, ff=8192, experts=8, top=2, eff=2048, sff=2048, vocab=32000),
+}
+
+
+def mefurax_config(s, span=1024):
+    layers = []
+    for i, ch in enumerate(s["pattern"]):
+        mlp = {"kind": "dense", "ff": s["ff"]} if i == 0 else {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]},
+                                                               "expert": {"ff": s["eff"]}, "shared": {"ff": s["sff"]}}
+        m = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "mask": {"size": span}, "scale": 128 ** -0.5, "v_mix": True}
+        if ch == "a":
+            m["conv"] = 4
+        else:
+            m.update(rot={"dims": 64, "base": 500000.0}, softcap=30.0)
+        layers.append({"type": "attention" if ch == "a" else "attention_2", "mixer": m, "mlp": mlp})
+    return {"architecture": "Mefurax", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6}, "postln_alpha": 2.0, "layers": layers}
+
+
+def lazilorn_feeder(cfg, seed, tensor_shapes=None):
     """upload(name, type, ne, data) for every tensor of cfg: bf16 bit patterns of N(0, 1/fan_in) matrices, f32 vectors."""
     import llama_gguf_b200 as B
     from llama_gguf_b200.safetensors_io import bf16_bits
-    from llama_gguf_b200.lazilorn import tensor_shapes
+    if tensor_shapes is None:
+        from llama_gguf_b200.lazilorn import tensor_shapes
 
     def feed(upload):
         rng = np.random.default_rng(seed)
@@ -54,15 +78,21 @@ def lazilorn_feeder(cfg, seed):
                 a = rng.uniform(1.0, 4.0, shape)
             elif last in ("A_log", "dt_bias", "b") and len(shape) == 1:
                 a = rng.uniform(-2.0, 0.5, shape)
+            elif last in ("norm1", "norm2", "vmix") and cfg["architecture"] == "Mefurax" or (name == "final.norm" and cfg["architecture"] == "Mefurax"):
+                a = 0.1 * rng.standard_normal(shape) + (0.4 if last == "vmix" else 0.0)
             else:
                 a = 1.0 + 0.1 * rng.standard_normal(shape)
-            upload(name, B.F32, list(reversed(shape)), np.ascontiguousarray(a, dtype=np.float32))
+            upload(name, B.F32, list(reversed(shape)) if shape else [1], np.ascontiguousarray(a, dtype=np.float32).reshape(shape if shape else (1,)))
     return feed
 
 
+def design_module(cfg):
+    from llama_gguf_b200 import lazilorn, mefurax
+    return {"Lazilorn": lazilorn, "Mefurax": mefurax}[cfg["architecture"]]
+
+
 def n_params(cfg):
-    from llama_gguf_b200.lazilorn import tensor_shapes
-    return int(sum(np.prod(s) for n, s in tensor_shapes(cfg).items() if n != "embed"))
+    return int(sum(np.prod(s) for n, s in design_module(cfg).tensor_shapes(cfg).items() if n != "embed"))
 
 
 def timed(fn, warm, reps):
@@ -76,9 +106,9 @@ def timed(fn, warm, reps):
 
 def bench_lazilorn(cfg, args, max_seq):
     import llama_gguf_b200 as B
-    from llama_gguf_b200 import lazilorn
-    program, layers = lazilorn.parse_config(cfg, max_seq, max(args.batch, 1) + 1, "bfloat16")
-    gpu = B.LayerProgramInference(program, layers, feeder=lazilorn_feeder(cfg, args.seed))
+    mod = design_module(cfg)
+    program, layers = mod.parse_config(cfg, max_seq, max(args.batch, 1) + 1, "bfloat16")
+    gpu = B.LayerProgramInference(program, layers, feeder=lazilorn_feeder(cfg, args.seed, mod.tensor_shapes))
     V = cfg["vocab"]
     rng = np.random.default_rng(args.seed + 1)
     out = {}
@@ -144,8 +174,10 @@ def bench_llama(s, n_layers, ffn, args, max_seq):
 def main(args):
     import llama_gguf_b200 as B
     if B.device_count() == 0:
-        print("bench.py --design lazilorn: no CUDA device", file=sys.stderr)
+        print("bench.py --design: no CUDA device", file=sys.stderr)
         return 2
+    if args.design == "mefurax":
+        return main_mefurax(args)
     sizes = [x for x in (args.sizes.split(",") if args.sizes else SIZES) if x]
     max_seq = max(args.prefill_len, args.prompt_len + args.warmup + args.steps + 8) + 8
     res = {}
@@ -164,4 +196,30 @@ def main(args):
     print(json.dumps({"bench": "design", "design": "lazilorn", "unit": "tok/s", "prefill_len": args.prefill_len, "prompt_len": args.prompt_len,
                       "batch": args.batch, "steps": args.steps, "warmup": args.warmup, "timing": "host wall clock around the library calls",
                       "dtype": "bf16 (lazilorn) / Q8_0 (llama)", "data": "synthetic", "sizes": res}))
+    return 0
+
+
+def main_mefurax(args):
+    sizes = [x for x in (args.sizes.split(",") if args.sizes else MEFURAX_SIZES) if x]
+    max_seq = max(args.prefill_len, args.prompt_len + args.warmup + args.steps + 8) + 8
+    res = {}
+    for name in sizes:
+        s = MEFURAX_SIZES[name]
+        cfg = mefurax_config(s)
+        params = n_params(cfg)
+        # parameters a token multiplies with: every mixer, the dense layer, router + `top` experts + the always-on expert of the others
+        w, L = s["width"], len(s["pattern"])
+        active = params - (L - 1) * (s["experts"] - s["top"]) * 2 * w * s["eff"]
+        attn = w * w * 2 + 2 * w * s["kv_heads"] * 128
+        ffn = max(256, int(round(((active - s["vocab"] * w) / L - attn) / (3 * w) / 256)) * 256)
+        r = {"params_without_embedding": params, "active_params_without_embedding": active, "layers": s["pattern"],
+             "mefurax_bf16": bench_lazilorn(cfg, args, max_seq)}
+        print(name, json.dumps(r), file=sys.stderr, flush=True)
+        r["lazilorn_bf16"] = bench_lazilorn(lazilorn_config(SIZES[name]), args, max_seq)
+        r["llama_q8_0"] = dict(bench_llama(s, L, ffn, args, max_seq), ffn=ffn)
+        res[name] = r
+        print(name, json.dumps(r), file=sys.stderr, flush=True)
+    print(json.dumps({"bench": "design", "design": "mefurax", "unit": "tok/s", "prefill_len": args.prefill_len, "prompt_len": args.prompt_len,
+                      "batch": args.batch, "steps": args.steps, "warmup": args.warmup, "timing": "host wall clock around the library calls",
+                      "dtype": "bf16 (mefurax, lazilorn) / Q8_0 (llama, sized to mefurax's active parameters)", "data": "synthetic", "sizes": res}))
     return 0

@@ -127,12 +127,26 @@ __device__ __forceinline__ void epi_store(void* Y, size_t idx, float v) {
     }
 }
 
+// the output row `off` elements on (f32 for the store / add epilogues, the compute type for relu^2)
+template <typename T, int EPI>
+__device__ __forceinline__ void* seg_rows(void* Y, size_t off) {
+    return EPI == EPI_RELU2 ? (void*)(reinterpret_cast<T*>(Y) + off) : (void*)(reinterpret_cast<float*>(Y) + off);
+}
 constexpr int GB = 64, GK = 16;
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) lp_gemm_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int ldw, void* __restrict__ Y,
-                                                      int ldy, int R, int N, int K, float alpha) {
+                                                      int ldy, int R, int N, int K, float alpha, const int* __restrict__ seg, size_t w_zstride) {
     __shared__ float As[GK][GB + 4];
     __shared__ float Bs[GK][GB + 4];
+    if (seg) {   // grid.z = group: rows [seg[0], seg[0] + seg[1]) of X and Y, known on the device only (R is the launch's upper bound),
+                 // against the group's own weight matrix
+        seg += 2 * blockIdx.z;
+        W += blockIdx.z * w_zstride;
+        X += (size_t)seg[0] * ldx;
+        Y = seg_rows<T, EPI>(Y, (size_t)seg[0] * ldy);
+        R = seg[1];
+        if ((int)blockIdx.y * GB >= R) return;
+    }
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int r0 = blockIdx.y * GB, n0 = blockIdx.x * GB;
     const int lr = tid >> 2, lk = (tid & 3) * 4;
@@ -211,8 +225,18 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
 
 template <int TN, int EPI>
 __global__ void __launch_bounds__(128) lp_gemm_tc_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
-                                                         void* __restrict__ Y, int ldy, int R, int N, int K, float alpha, int* err) {
+                                                         void* __restrict__ Y, int ldy, int R, int N, int K, float alpha, int* err,
+                                                         const int* __restrict__ seg, size_t w_zstride) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
+    if (seg) {   // grid.z = group: rows [seg[0], seg[0] + seg[1]) of X and Y, known on the device only, against the group's own weight
+                 // matrix; a CTA beyond the rows leaves before it holds anything
+        seg += 2 * blockIdx.z;
+        W += blockIdx.z * w_zstride;
+        X += (size_t)seg[0] * ldx;
+        Y = seg_rows<bf16, EPI>(Y, (size_t)seg[0] * ldy);
+        R = seg[1];
+        if ((int)blockIdx.y * TN >= R) return;
+    }
     __shared__ __align__(8) unsigned long long s_bar[TC_STAGES];
     __shared__ uint32_t s_tmem;
     constexpr int kStage = (TC_M + TN) * 128;
@@ -1267,7 +1291,9 @@ struct LpModel {
     size_t meta_bytes = 0;
     float *x = nullptr, *P = nullptr, *qbuf = nullptr, *O = nullptr, *conv = nullptr, *logits = nullptr;
     float *y = nullptr, *vsrc = nullptr, *moe_w = nullptr, *moe_selw = nullptr;   // sublayer output (norm-after-sum layers), shared values, routing
-    int* moe_sel = nullptr;
+    int *moe_sel = nullptr, *moe_pos = nullptr, *moe_seg = nullptr;   // chosen experts per row; row of (token, choice) in expert order; {first, rows} per expert
+    void* moe_xp = nullptr;             // the tokens' rows gathered in expert order, compute type
+    float* moe_yp = nullptr;            // the experts' outputs in the same order
     int max_vsrc = 0, max_experts = 0, max_top = 0;
     void *hn = nullptr, *act_a = nullptr, *hw = nullptr;
     int* pick = nullptr;
@@ -1370,7 +1396,8 @@ void launch(LpModel* m, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sm
 
 // The tensor-core GEMM takes bf16 operands whose rows are 16-byte aligned (K and the row pitches multiples of 8).
 template <int TN>
-bool tc_launch(LpModel* m, const bf16* x, int ldx, const bf16* w, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
+bool tc_launch(LpModel* m, const bf16* x, int ldx, const bf16* w, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg,
+               int groups, size_t zs) {
     const size_t smem = (size_t)TC_STAGES * (TC_M + TN) * 128 + 1024;
     static bool once[3][64] = {};
     int dev = 0;
@@ -1384,56 +1411,71 @@ bool tc_launch(LpModel* m, const bf16* x, int ldx, const bf16* w, int N, int K, 
         if (dev >= 0 && dev < 64) once[e][dev] = true;
         return true;
     };
-    dim3 grid((N + TC_M - 1) / TC_M, (R + TN - 1) / TN), block(128);
+    dim3 grid((N + TC_M - 1) / TC_M, (R + TN - 1) / TN, groups), block(128);
     if (epi == EPI_STORE) {
         if (!prep(lp_gemm_tc_kernel<TN, EPI_STORE>, 0)) return false;
-        launch(m, lp_gemm_tc_kernel<TN, EPI_STORE>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, m->tc_err);
+        launch(m, lp_gemm_tc_kernel<TN, EPI_STORE>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, m->tc_err, seg, zs);
     } else if (epi == EPI_ADD) {
         if (!prep(lp_gemm_tc_kernel<TN, EPI_ADD>, 1)) return false;
-        launch(m, lp_gemm_tc_kernel<TN, EPI_ADD>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, m->tc_err);
+        launch(m, lp_gemm_tc_kernel<TN, EPI_ADD>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, m->tc_err, seg, zs);
     } else {
         if (!prep(lp_gemm_tc_kernel<TN, EPI_RELU2>, 2)) return false;
-        launch(m, lp_gemm_tc_kernel<TN, EPI_RELU2>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, m->tc_err);
+        launch(m, lp_gemm_tc_kernel<TN, EPI_RELU2>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, m->tc_err, seg, zs);
     }
     return true;
 }
-bool tc_gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
+bool tc_gemm(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg,
+             int groups, size_t zs) {
     if (m->f32 || !m->use_tc || R < m->tc_min_rows) return false;
-    if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return false;
+    if (K % 8 || ldx % 8 || ldw % 8 || zs % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return false;
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
-    if (R <= 64) return tc_launch<64>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);
-    if (R <= 128) return tc_launch<128>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);   // (wider token tiles move fewer operand bytes per FLOP: measured 2.5x on a 2048 x 8192 x 2048 product even at 128 CTAs)
-    return tc_launch<256>(m, x, ldx, w, N, K, Y, ldy, R, alpha, epi);
+    if (R <= 64) return tc_launch<64>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, zs);
+    if (R <= 128) return tc_launch<128>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, zs);   // (wider token tiles move fewer operand bytes per FLOP: measured 2.5x on a 2048 x 8192 x 2048 product even at 128 CTAs)
+    return tc_launch<256>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, zs);
 }
 
 // Y = epi(alpha X W^T): rows of the step against a [N][K] matrix in the compute type
 template <typename T>
-void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
+void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg = nullptr,
+            int groups = 1, size_t zs = 0) {
     const T* x = (const T*)X;
     const T* w = (const T*)W;
-    if (R <= 2 * GV_ROWS) {
+    if (R <= 2 * GV_ROWS && !seg) {
         constexpr int VN = Vec8<T>::N;
-        const int vec_ok = (K % VN == 0 && ldx % VN == 0 && ((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0) ? 1 : 0;
+        const int vec_ok = (K % VN == 0 && ldx % VN == 0 && ldw % VN == 0 && ((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0) ? 1 : 0;
         // a few blocks per SM, each walking its share of the output columns with the activation rows staged once
         dim3 grid(std::min((N + 7) / 8, 4 * 148)), block(256);
         const size_t xbytes = (size_t)R * K * sizeof(T);
         const int stage = (vec_ok && sizeof(T) * VN == 16 && xbytes <= 48 * 1024) ? 1 : 0;
         const size_t smem = stage ? xbytes : 0;
-        if (epi == EPI_STORE) launch(m, lp_gemv_kernel<T, EPI_STORE>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok, stage);
-        else if (epi == EPI_ADD) launch(m, lp_gemv_kernel<T, EPI_ADD>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok, stage);
-        else launch(m, lp_gemv_kernel<T, EPI_RELU2>, grid, block, smem, x, ldx, w, K, Y, ldy, R, N, K, alpha, vec_ok, stage);
+        if (epi == EPI_STORE) launch(m, lp_gemv_kernel<T, EPI_STORE>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage);
+        else if (epi == EPI_ADD) launch(m, lp_gemv_kernel<T, EPI_ADD>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage);
+        else launch(m, lp_gemv_kernel<T, EPI_RELU2>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage);
         return;
     }
-    if (tc_gemm(m, X, ldx, W, N, K, Y, ldy, R, alpha, epi)) return;
-    dim3 grid((N + GB - 1) / GB, (R + GB - 1) / GB), block(256);
-    if (epi == EPI_STORE) launch(m, lp_gemm_kernel<T, EPI_STORE>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha);
-    else if (epi == EPI_ADD) launch(m, lp_gemm_kernel<T, EPI_ADD>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha);
-    else launch(m, lp_gemm_kernel<T, EPI_RELU2>, grid, block, 0, x, ldx, w, K, Y, ldy, R, N, K, alpha);
+    if (tc_gemm(m, X, ldx, W, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, zs)) return;
+    dim3 grid((N + GB - 1) / GB, (R + GB - 1) / GB, groups), block(256);
+    if (epi == EPI_STORE) launch(m, lp_gemm_kernel<T, EPI_STORE>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, zs);
+    else if (epi == EPI_ADD) launch(m, lp_gemm_kernel<T, EPI_ADD>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, zs);
+    else launch(m, lp_gemm_kernel<T, EPI_RELU2>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, zs);
 }
 void gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
-    if (m->f32) gemm_t<float>(m, X, ldx, W, N, K, Y, ldy, R, alpha, epi);
-    else gemm_t<bf16>(m, X, ldx, W, N, K, Y, ldy, R, alpha, epi);
+    if (m->f32) gemm_t<float>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi);
+    else gemm_t<bf16>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi);
+}
+// `groups` products in one launch (grid.z): group g multiplies rows [seg[2g], seg[2g] + seg[2g + 1]) of X -- the counts live on the
+// device, R is their upper bound -- with the matrix at Wm + g * zs elements, whose rows are ldw apart (contiguous matrices: ldw = K,
+// zs = N K; column blocks of one wide matrix: ldw = its width, zs = K), into the same rows of Y.
+void gemm_grouped(LpModel* m, const void* X, int ldx, const void* Wm, int ldw, size_t zs, int groups, int N, int K, void* Y, int ldy, int R, int epi,
+                  const int* seg) {
+    if (m->f32) gemm_t<float>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi, seg, groups, zs);
+    else gemm_t<bf16>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi, seg, groups, zs);
+}
+// One product with a weight matrix whose rows are `ldw` apart (a block of columns of a wider matrix).
+void gemm_ld(LpModel* m, const void* X, int ldx, const void* Wm, int ldw, int N, int K, void* Y, int ldy, int R, int epi) {
+    if (m->f32) gemm_t<float>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi);
+    else gemm_t<bf16>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi);
 }
 
 void rmsnorm(LpModel* m, float* x, const float* add, const float* w, void* out, const int* gather, int rows) {
@@ -1870,6 +1912,7 @@ int lp_finalize(LpModel* m, std::string* err) {
             m->tensors[pre + "mlp.down_cat"] = t;
             m->max_act = std::max(m->max_act, L.k_down);
             m->max_in = std::max(m->max_in, L.n_up);
+            m->weight_bytes -= (size_t)(e.experts - e.top) * 2 * e.expert_ff * W * es;   // a token reads its chosen experts only
             m->max_experts = std::max(m->max_experts, e.experts);
             m->max_top = std::max(m->max_top, e.top);
         } else if (L.d.ff > 0) {
@@ -1947,7 +1990,7 @@ void lp_destroy(LpModel* m) {
     for (SlotMem& s : m->pool) { cudaFree(s.kv); cudaFree(s.rec); }
     for (void* ptr : {(void*)m->inv_freq, (void*)m->d_meta, (void*)m->x, (void*)m->P, (void*)m->qbuf, (void*)m->O, (void*)m->conv, (void*)m->logits,
                       m->hn, m->act_a, m->hw, (void*)m->pick, (void*)m->taps, (void*)m->y, (void*)m->vsrc, (void*)m->moe_w, (void*)m->moe_selw,
-                      (void*)m->moe_sel})
+                      (void*)m->moe_sel, (void*)m->moe_pos, (void*)m->moe_seg, m->moe_xp, (void*)m->moe_yp})
         cudaFree(ptr);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_logits) cudaFreeHost(m->h_logits);
@@ -2013,12 +2056,16 @@ int ensure_scratch(LpModel* m, int R, int n_runs, int n_want, std::string* err) 
         if ((rc = grow(&m->conv, (size_t)cap * std::max(m->max_conv, 1) * 4, err))) return rc;
         if ((rc = grow(&m->hn, (size_t)cap * W * es, err))) return rc;
         if ((rc = grow(&m->act_a, (size_t)cap * m->max_act * es, err))) return rc;
-        if (m->p.post_norm && (rc = grow(&m->y, (size_t)cap * W * 4, err))) return rc;
+        if ((m->p.post_norm || m->max_experts > 0) && (rc = grow(&m->y, (size_t)cap * W * 4, err))) return rc;
         if (m->max_vsrc > 0 && (rc = grow(&m->vsrc, (size_t)cap * m->max_vsrc * 4, err))) return rc;
         if (m->max_experts > 0) {
             if ((rc = grow(&m->moe_w, (size_t)cap * m->max_experts * 4, err))) return rc;
             if ((rc = grow(&m->moe_selw, (size_t)cap * m->max_top * 4, err))) return rc;
             if ((rc = grow(&m->moe_sel, (size_t)cap * m->max_top * 4, err))) return rc;
+            if ((rc = grow(&m->moe_pos, (size_t)cap * m->max_top * 4, err))) return rc;
+            if ((rc = grow(&m->moe_seg, (size_t)(2 * m->max_experts + 2) * 4, err))) return rc;
+            if ((rc = grow(&m->moe_xp, (size_t)cap * m->max_top * W * es, err))) return rc;
+            if ((rc = grow(&m->moe_yp, (size_t)cap * m->max_top * W * 4, err))) return rc;
         }
         m->cap_rows = cap;
     }
@@ -2172,15 +2219,55 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             project_out(m->act_a, ldo, L.wo_delta, L.norm1);
         }
         if (L.d.ff_kind == B200_FF_MOE) {
-            // one product for [router | every expert's up | the always-on expert's up] (f32 out), the router's choice per row, the
-            // activations times their expert's weight (0 for experts that were not chosen), one product with the down matrices side by side
+            // The operand is m->hn in both layer forms; the router's rows come first in w_up ([router | e0 up | ... | always-on up]).
+            // Router logits (f32) -> the choice per row -> the experts -> m->y -> the residual.
             const b200_moe_desc& e = L.d.moe;
-            project_in(nullptr, L.norm2, L.w_up, L.n_up, m->P, L.n_up, EPI_STORE);
-            launch(m, lp_moe_route_kernel, dim3((R + 3) / 4), dim3(128), 0, (const float*)m->P, L.n_up, e.experts, e.top, m->moe_w, m->moe_sel, m->moe_selw, R);
-            const unsigned nb = (unsigned)(((size_t)R * L.k_down + 255) / 256);
-            if (m->f32) launch(m, lp_moe_act_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, e.experts, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (float*)m->act_a, R);
-            else launch(m, lp_moe_act_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, e.experts, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (bf16*)m->act_a, R);
-            project_out(m->act_a, L.k_down, L.w_down, L.norm2);
+            const size_t es = elt(m);
+            if (!post) rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
+            gemm(m, m->hn, W, L.w_up, e.experts, W, m->P, e.experts, R, 1.0f, EPI_STORE);
+            launch(m, lp_moe_route_kernel, dim3((R + 3) / 4), dim3(128), 0, (const float*)m->P, e.experts, e.experts, e.top, m->moe_w, m->moe_sel, m->moe_selw, R);
+            const int vn = m->f32 ? 4 : 8;
+            const size_t hbytes = (size_t)R * W * es;
+            const uint8_t* up_experts = (const uint8_t*)L.w_up + (size_t)e.experts * W * es;
+            if (m->use_fuse && R <= 2 * GV_ROWS && W % vn == 0 && e.expert_ff % vn == 0 && e.shared_ff % vn == 0 && hbytes <= 48 * 1024) {
+                // few rows (decoding): kernels that walk each row's choices and read those experts' weights only
+                const int per_row = e.top * e.expert_ff + e.shared_ff;
+                dim3 ugrid(std::min((R * per_row + 7) / 8, 8 * 148)), dgrid(std::min((R * W + 7) / 8, 8 * 148));
+                if (m->f32) {
+                    launch(m, lp_moe_up_sel_kernel<float>, ugrid, dim3(256), hbytes, (const float*)m->hn, (const float*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (float*)m->act_a);
+                    launch(m, lp_moe_down_sel_kernel<float>, dgrid, dim3(256), 0, (const float*)m->act_a, (const float*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y);
+                } else {
+                    launch(m, lp_moe_up_sel_kernel<bf16>, ugrid, dim3(256), hbytes, (const bf16*)m->hn, (const bf16*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (bf16*)m->act_a);
+                    launch(m, lp_moe_down_sel_kernel<bf16>, dgrid, dim3(256), 0, (const bf16*)m->act_a, (const bf16*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y);
+                }
+            } else if (m->use_fuse && R > 2 * GV_ROWS) {
+                // many rows: the (token, choice) pairs in expert order, one product pair per expert over its block of rows (the row
+                // counts stay on the device), the always-on expert over all rows, then the weighted sum per token
+                const int pairs = R * e.top;
+                launch(m, lp_moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * e.experts * 4, (const int*)m->moe_sel, pairs, e.experts, m->moe_seg, m->moe_pos);
+                if (m->f32) launch(m, lp_moe_gather_kernel<float>, dim3(pairs), dim3(128), 0, (const float*)m->hn, (const int*)m->moe_pos, e.top, W, (float*)m->moe_xp);
+                else launch(m, lp_moe_gather_kernel<bf16>, dim3(pairs), dim3(128), 0, (const bf16*)m->hn, (const int*)m->moe_pos, e.top, W, (bf16*)m->moe_xp);
+                const uint8_t* down = (const uint8_t*)L.w_down;
+                uint8_t* act_sh = (uint8_t*)m->act_a + (size_t)pairs * e.expert_ff * es;     // the always-on expert's activations behind the others
+                gemm_grouped(m, m->moe_xp, W, up_experts, W, (size_t)e.expert_ff * W, e.experts, e.expert_ff, W, m->act_a, e.expert_ff, R, EPI_RELU2, m->moe_seg);
+                gemm_grouped(m, m->act_a, e.expert_ff, down, L.k_down, (size_t)e.expert_ff, e.experts, W, e.expert_ff, m->moe_yp, W, R, EPI_STORE, m->moe_seg);
+                if (e.shared_ff > 0) {
+                    gemm(m, m->hn, W, up_experts + (size_t)e.experts * e.expert_ff * W * es, e.shared_ff, W, act_sh, e.shared_ff, R, 1.0f, EPI_RELU2);
+                    gemm_ld(m, act_sh, e.shared_ff, down + (size_t)e.experts * e.expert_ff * es, L.k_down, W, e.shared_ff, m->y, W, R, EPI_STORE);
+                }
+                launch(m, lp_moe_combine_kernel, dim3(R), dim3(256), 0, (const float*)m->moe_yp, (const int*)m->moe_pos, (const float*)m->moe_selw, e.top, W, e.shared_ff > 0 ? 1 : 0, m->y);
+            } else {
+                // the plain form: every expert's up projection for every row, activations times their expert's weight (0 for experts
+                // that were not chosen), one product with the down matrices side by side
+                const int n_exp = L.n_up - e.experts;
+                gemm(m, m->hn, W, up_experts, n_exp, W, m->P, n_exp, R, 1.0f, EPI_STORE);
+                const unsigned nb = (unsigned)(((size_t)R * L.k_down + 255) / 256);
+                if (m->f32) launch(m, lp_moe_act_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (float*)m->act_a, R);
+                else launch(m, lp_moe_act_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (bf16*)m->act_a, R);
+                gemm(m, m->act_a, L.k_down, L.w_down, W, L.k_down, m->y, W, R, 1.0f, EPI_STORE);
+            }
+            if (post) cast_x(m->y, L.norm2);
+            else launch(m, lp_add_rows_kernel, dim3((unsigned)(((size_t)R * W + 255) / 256)), dim3(256), 0, m->x, (const float*)m->y, (size_t)R * W);
         } else if (L.d.ff > 0 && L.d.ff_kind == B200_FF_GATED_GELU) {
             project_in(nullptr, L.norm2, L.w_up, L.n_up, m->P, L.n_up, EPI_STORE);
             const unsigned nb = (unsigned)(((size_t)R * L.d.ff + 255) / 256);

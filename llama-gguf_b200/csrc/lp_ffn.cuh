@@ -109,3 +109,128 @@ __global__ void lp_moe_act_kernel(const float* __restrict__ P, int ldp, int off,
     }
     out[i] = from_f<OutT>(v);
 }
+
+// Few rows (decoding): only the chosen experts' weights are read.  up_cat holds [router | e0 up | e1 up | ... | always-on up] rows of
+// `width` columns; segment k < top of a row's activations belongs to expert sel[r][k], segment `top` to the always-on expert.
+//   act[r][k eff + n] = relu(up_e[n] . h_r)^2 * selw[r][k]        act[r][top eff + n] = relu(up_shared[n] . h_r)^2
+// One warp per (row, segment, n); h rows are staged in shared memory once per block.
+template <typename T>
+__global__ void __launch_bounds__(256) lp_moe_up_sel_kernel(const T* __restrict__ H, const T* __restrict__ up_cat, const int* __restrict__ sel,
+                                                            const float* __restrict__ selw, int E, int top, int eff, int sff, int width, int R,
+                                                            T* __restrict__ act) {
+    extern __shared__ __align__(16) uint8_t mu_smem[];
+    T* hs = reinterpret_cast<T*>(mu_smem);
+    constexpr int VN = Vec8<T>::N;
+    for (int i = threadIdx.x; i < R * width / VN; i += blockDim.x)
+        *reinterpret_cast<uint4*>(hs + (size_t)i * VN) = *reinterpret_cast<const uint4*>(H + (size_t)i * VN);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int per_row = top * eff + sff;
+    const int total = R * per_row;
+    for (int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); o < total; o += gridDim.x * (blockDim.x >> 5)) {
+        const int r = o / per_row, c = o - r * per_row;
+        const int k = c < top * eff ? c / eff : top;
+        const int n = c - k * eff;
+        const int e = k < top ? sel[(size_t)r * top + k] : E;
+        const T* wr = up_cat + ((size_t)E + (size_t)e * eff + n) * width;
+        const T* hr = hs + (size_t)r * width;
+        float acc = 0.0f;
+        for (int i = lane * VN; i < width; i += 32 * VN) {
+            float wv[VN], xv[VN];
+            Vec8<T>::load(wr + i, wv);
+            Vec8<T>::load(hr + i, xv);
+#pragma unroll
+            for (int j = 0; j < VN; j++) acc = fmaf(wv[j], xv[j], acc);
+        }
+        acc = wsum(acc);
+        if (lane == 0) {
+            const float z = fmaxf(acc, 0.0f);
+            act[o] = from_f<T>(z * z * (k < top ? selw[(size_t)r * top + k] : 1.0f));
+        }
+    }
+}
+
+// y[r][c] = sum over the row's segments of down_e[c] . act segment; down_cat is [width][E eff + sff].  One warp per (row, c).
+template <typename T>
+__global__ void __launch_bounds__(256) lp_moe_down_sel_kernel(const T* __restrict__ act, const T* __restrict__ down_cat, const int* __restrict__ sel,
+                                                              int E, int top, int eff, int sff, int width, int R, float* __restrict__ y) {
+    constexpr int VN = Vec8<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int per_row = top * eff + sff, kd = E * eff + sff;
+    for (int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); o < R * width; o += gridDim.x * (blockDim.x >> 5)) {
+        const int r = o / width, c = o - r * width;
+        const T* ar = act + (size_t)r * per_row;
+        const T* dr = down_cat + (size_t)c * kd;
+        float acc = 0.0f;
+        for (int k = 0; k <= top; k++) {
+            const int e = k < top ? sel[(size_t)r * top + k] : E;
+            const int len = k < top ? eff : sff;
+            const T* w = dr + (size_t)e * eff;
+            const T* a = ar + (size_t)k * eff;
+            for (int i = lane * VN; i < len; i += 32 * VN) {
+                float wv[VN], xv[VN];
+                Vec8<T>::load(w + i, wv);
+                Vec8<T>::load(a + i, xv);
+#pragma unroll
+                for (int j = 0; j < VN; j++) acc = fmaf(wv[j], xv[j], acc);
+            }
+        }
+        acc = wsum(acc);
+        if (lane == 0) y[o] = acc;
+    }
+}
+
+// Many rows: the (token, choice) pairs are put in expert order, so that every expert multiplies a contiguous block of rows.
+// One block: counts per expert, their running sum (seg[e] = {first row, rows}), then every pair takes the next free row of its
+// expert (pos[r top + k]).  Which pair of an expert gets which row does not matter: a row's result does not depend on its place.
+__global__ void __launch_bounds__(1024) lp_moe_sort_kernel(const int* __restrict__ sel, int n_pairs, int E, int* __restrict__ seg, int* __restrict__ pos) {
+    extern __shared__ int ms[];          // [E] counts, then [E] cursors
+    int* cnt = ms;
+    int* cur = ms + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&cnt[sel[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; e++) {
+            seg[2 * e] = at;
+            seg[2 * e + 1] = cnt[e];
+            cur[e] = at;
+            at += cnt[e];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) pos[i] = atomicAdd(&cur[sel[i]], 1);
+}
+
+// Xp[pos[i]] = H[i / top]: one block per pair
+template <typename T>
+__global__ void lp_moe_gather_kernel(const T* __restrict__ H, const int* __restrict__ pos, int top, int width, T* __restrict__ Xp) {
+    const int i = blockIdx.x;
+    const T* src = H + (size_t)(i / top) * width;
+    T* dst = Xp + (size_t)pos[i] * width;
+    constexpr int VN = Vec8<T>::N;
+    if (width % VN == 0) {
+        for (int c = threadIdx.x; c < width / VN; c += blockDim.x) reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+    }
+}
+
+// y[r] (+)= sum_k selw[r][k] Yp[pos[r top + k]], choices in the order they were taken; add = 1 when y already holds the always-on
+// expert's output
+__global__ void lp_moe_combine_kernel(const float* __restrict__ Yp, const int* __restrict__ pos, const float* __restrict__ selw, int top, int width,
+                                      int add, float* __restrict__ y) {
+    const int r = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = add ? y[(size_t)r * width + c] : 0.0f;
+        for (int k = 0; k < top; k++) acc = fmaf(selw[(size_t)r * top + k], Yp[(size_t)pos[(size_t)r * top + k] * width + c], acc);
+        y[(size_t)r * width + c] = acc;
+    }
+}
+
+__global__ void lp_add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += y[i];
+}

@@ -74,10 +74,11 @@ def write_safetensors(path, tensors):
     """tensors: name -> ndarray (float32 -> F32, uint16 -> BF16 bit patterns, int32 -> I32).  For tests and synthetic models."""
     header, blobs, off = {}, [], 0
     for name, a in tensors.items():
+        shape = list(np.shape(a))          # (a scalar keeps its empty shape: ascontiguousarray would make it [1])
         a = np.ascontiguousarray(a)
         dt = {"float32": "F32", "uint16": "BF16", "int32": "I32"}[a.dtype.name]
         raw = a.tobytes()
-        header[name] = {"dtype": dt, "shape": list(a.shape), "data_offsets": [off, off + len(raw)]}
+        header[name] = {"dtype": dt, "shape": shape, "data_offsets": [off, off + len(raw)]}
         blobs.append(raw)
         off += len(raw)
     hj = json.dumps(header, separators=(",", ":")).encode()

@@ -545,3 +545,39 @@ def test_trace_runner_on_a_model_folder(b200, tmp_path):
     assert S.rel_err(got[1], wb[5:6]) < F32_TOL
     assert S.rel_err(got[2], np.stack([wa[16], wb[6]])) < F32_TOL
     assert S.rel_err(got[3], wa[18:19]) < F32_TOL
+
+
+def test_decode_kernels_for_few_rows_against_the_many_row_path(b200, monkeypatch):
+    # decoding reads only the chosen experts' weights (a kernel per projection that walks the router's picks); B200_LP_FUSE=0 sends
+    # the same rows through the products over all experts.  Both against the oracle, in a batch whose members sit at different
+    # positions, in f32; and against each other in bf16.
+    cfg = S.config([S.layer_b(mlp=S.moe(experts=6, top=2, ff=24, shared=16)), S.layer_a(conv=4, mlp=S.moe(experts=3, top=3, ff=8, shared=0)),
+                    S.layer_b(chunk=4, mlp=S.moe(experts=4, top=1, ff=32, shared=8))])
+    w = S.random_weights(cfg, 53)
+    ref = O.Model(cfg, w)
+    prompts = [tokens(n, cfg["vocab"], 60 + n) for n in (3, 19, 1)]
+    tails = [tokens(12, cfg["vocab"], 70 + i) for i in range(3)]
+    states = [ref.new_state() for _ in prompts]
+    for st, pr in zip(states, prompts):
+        ref.step(st, pr)
+    want = [[ref.step(states[i], [tails[i][k]])[0] for i in range(3)] for k in range(12)]
+    bf = {}
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("B200_LP_FUSE", fuse)
+        for compute in ("float32", "bfloat16"):
+            gpu = S.gpu_model(cfg, w, compute)
+            try:
+                gpu.step([(i, pr) for i, pr in enumerate(prompts)])
+                rows = []
+                for k in range(12):
+                    lg = gpu.decode_batch([0, 1, 2], [tails[i][k] for i in range(3)])
+                    rows.append(lg)
+                    if compute == "float32":
+                        for i in range(3):
+                            assert S.rel_err(lg[i], want[k][i]) < F32_TOL, (fuse, k, i)
+                if compute == "bfloat16":
+                    bf[fuse] = np.concatenate(rows)
+            finally:
+                gpu.close()
+    d = np.array([S.rel_err(bf["1"][i], bf["0"][i]) for i in range(len(bf["1"]))])
+    assert np.median(d) < 2e-2 and (d < 2e-2).mean() > 0.9
