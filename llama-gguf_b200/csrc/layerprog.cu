@@ -376,9 +376,11 @@ template <> struct Vec8<float> {
         o[0] = u.x; o[1] = u.y; o[2] = u.z; o[3] = u.w;
     }
 };
+#include "lp_rows_tail.cuh"
+
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int ldw, void* __restrict__ Y,
-                                                      int ldy, int R, int N, int K, float alpha, int vec_ok, int stage) {
+                                                      int ldy, int R, int N, int K, float alpha, int vec_ok, int stage, RowsTail tail) {
     extern __shared__ __align__(16) uint8_t gv_smem[];
     const int lane = threadIdx.x & 31;
     constexpr int VN = Vec8<T>::N;
@@ -429,6 +431,7 @@ __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, i
         }
     }
     }
+    if (tail.on) rows_tail<T>(tail);
 }
 
 // The same for a normed input: the block first norms the (few) rows of the f32 residual stream into shared memory -- rms over the
@@ -1317,6 +1320,7 @@ struct LpModel {
     int tc_min_rows = 17;
     int* tc_err = nullptr;
     int* h_tc_err = nullptr;
+    unsigned* tail_counter = nullptr;   // arrival counter of rows_tail (zero between kernels)
 };
 
 namespace {
@@ -1438,7 +1442,7 @@ bool tc_gemm(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, 
 // Y = epi(alpha X W^T): rows of the step against a [N][K] matrix in the compute type
 template <typename T>
 void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg = nullptr,
-            int groups = 1, size_t zs = 0) {
+            int groups = 1, size_t zs = 0, const RowsTail* tail = nullptr) {
     const T* x = (const T*)X;
     const T* w = (const T*)W;
     if (R <= 2 * GV_ROWS && !seg) {
@@ -1449,9 +1453,9 @@ void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, i
         const size_t xbytes = (size_t)R * K * sizeof(T);
         const int stage = (vec_ok && sizeof(T) * VN == 16 && xbytes <= 48 * 1024) ? 1 : 0;
         const size_t smem = stage ? xbytes : 0;
-        if (epi == EPI_STORE) launch(m, lp_gemv_kernel<T, EPI_STORE>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage);
-        else if (epi == EPI_ADD) launch(m, lp_gemv_kernel<T, EPI_ADD>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage);
-        else launch(m, lp_gemv_kernel<T, EPI_RELU2>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage);
+        if (epi == EPI_STORE) launch(m, lp_gemv_kernel<T, EPI_STORE>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage, tail ? *tail : RowsTail{});
+        else if (epi == EPI_ADD) launch(m, lp_gemv_kernel<T, EPI_ADD>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage, tail ? *tail : RowsTail{});
+        else launch(m, lp_gemv_kernel<T, EPI_RELU2>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage, tail ? *tail : RowsTail{});
         return;
     }
     if (tc_gemm(m, X, ldx, W, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, zs)) return;
@@ -1460,9 +1464,10 @@ void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, i
     else if (epi == EPI_ADD) launch(m, lp_gemm_kernel<T, EPI_ADD>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, zs);
     else launch(m, lp_gemm_kernel<T, EPI_RELU2>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, zs);
 }
-void gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi) {
-    if (m->f32) gemm_t<float>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi);
-    else gemm_t<bf16>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi);
+// tail: few rows only (the caller has checked R): the last block goes on with rows_tail
+void gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const RowsTail* tail = nullptr) {
+    if (m->f32) gemm_t<float>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi, nullptr, 1, 0, tail);
+    else gemm_t<bf16>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi, nullptr, 1, 0, tail);
 }
 // `groups` products in one launch (grid.z): group g multiplies rows [seg[2g], seg[2g] + seg[2g + 1]) of X -- the counts live on the
 // device, R is their upper bound -- with the matrix at Wm + g * zs elements, whose rows are ldw apart (contiguous matrices: ldw = K,
@@ -1969,6 +1974,7 @@ int lp_finalize(LpModel* m, std::string* err) {
     }
     LCU_ALLOC(cudaMalloc((void**)&m->tc_err, 256));
     LCU(cudaMemset(m->tc_err, 0, 256));
+    m->tail_counter = (unsigned*)(m->tc_err + 16);
     LCU_ALLOC(cudaHostAlloc((void**)&m->h_tc_err, 64, cudaHostAllocDefault));
     *m->h_tc_err = 0;
     m->finalized = true;
@@ -2150,8 +2156,24 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         if (post) gemm(m, m->hn, W, Wm, N, W, Y, ldy, R, 1.0f, epi);
         else norm_gemm(m, m->x, add, nullptr, nw, m->hn, Wm, N, Y, ldy, R, 1.0f, epi);
     };
-    auto project_out = [&](const void* X, int K, const void* Wm, const float* nw) {
-        if (post) {
+    // Few rows (decoding) in the norm-after-sum form: the kernel that writes m->y also does what follows it -- its last block norms the
+    // rows and, when `moe` follows, computes the router's logits and choices (rows_tail) -- instead of two or three more launches.
+    const bool few = post && m->use_fuse && R <= 2 * GV_ROWS;
+    auto make_tail = [&](const float* nw, const LayerPlan* moe) {
+        RowsTail t{};
+        t.on = 1; t.x = m->x; t.y = m->y; t.w = nw; t.xc = m->hn; t.width = W; t.R = R; t.alpha = p.residual_alpha; t.eps = p.norm_eps;
+        t.counter = m->tail_counter;
+        if (moe) {
+            t.router = moe->w_up; t.E = moe->d.moe.experts; t.top = moe->d.moe.top;
+            t.logits = m->P; t.wts = m->moe_w; t.sel = m->moe_sel; t.selw = m->moe_selw;
+        }
+        return t;
+    };
+    auto project_out = [&](const void* X, int K, const void* Wm, const float* nw, const LayerPlan* moe) {
+        if (few) {
+            const RowsTail t = make_tail(nw, moe);
+            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE, &t);
+        } else if (post) {
             gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE);
             cast_x(m->y, nw);
         } else gemm(m, X, K, Wm, W, K, m->x, W, R, 1.0f, EPI_ADD);
@@ -2160,6 +2182,10 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
     for (size_t run = 0; run < m->runs.size(); run++) {
         LayerPlan& L = m->plan[m->runs[run]];
         const float* add = m->run_pass[run] >= 0 ? loop_step + (size_t)m->run_pass[run] * W : nullptr;
+        // the few-row expert kernels (16-byte loads: sizes multiples of 8 / 4, the rows in shared memory)
+        const bool moe_sel_ok = L.d.ff_kind == B200_FF_MOE && m->use_fuse && R <= 2 * GV_ROWS && W % (m->f32 ? 4 : 8) == 0 &&
+                                L.d.moe.expert_ff % (m->f32 ? 4 : 8) == 0 && L.d.moe.shared_ff % (m->f32 ? 4 : 8) == 0 && (size_t)R * W * elt(m) <= 48 * 1024;
+        const LayerPlan* moe_next = (few && moe_sel_ok) ? &L : nullptr;      // the mixer's output kernel also routes
         project_in(add, L.norm1, L.w_in, L.n_in, m->P, L.n_in, EPI_STORE);
         if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) {
             AttnGeom ag = L.ag;
@@ -2170,11 +2196,12 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             PrepGeom pg = L.pg;
             pg.rec_off = m->run_rec_off[run];
             const size_t psmem = (size_t)(((pg.C + 3) & ~3) + pg.rot_dims) * 4;
+            const int shift = (m->use_fuse && max_len == 1) ? 1 : 0;   // one row per run: the row's block moves the run's tail on itself
             launch(m, lp_attn_prep2_kernel, dim3(R), dim3(256), psmem, sm, ag, pg, (const float*)m->P, L.n_in, L.qkv_bias, L.conv_w, L.qn, L.kn, L.rot_freq,
-                   L.vmix, m->vsrc, m->qbuf);
-            if (pg.taps > 1) launch(m, lp_attn_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, pg, (const float*)m->P, L.n_in, L.qkv_bias);
+                   L.vmix, m->vsrc, m->qbuf, shift);
+            if (pg.taps > 1 && !shift) launch(m, lp_attn_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, pg, (const float*)m->P, L.n_in, L.qkv_bias);
             if (!attn_tile(m, sm, ag, L.n_in, n_runs, max_len)) attn_rows(m, sm, ag, L, R);
-            project_out(m->act_a, ag.out_ld, L.wo, L.norm1);
+            project_out(m->act_a, ag.out_ld, L.wo, L.norm1, moe_next);
         } else if (L.d.mixer == B200_MIX_WINDOW_MEMORY) {
             AttnGeom ag = L.ag;
             ag.kv_off = m->run_kv_off[run];
@@ -2197,7 +2224,7 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             dim3 hgrid(R, (mg.H + 3) / 4);
             if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (float*)m->act_a + ag.H * ag.vdim, L.k_cat, L.d.mem_scale, R);
             else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (bf16*)m->act_a + ag.H * ag.vdim, L.k_cat, L.d.mem_scale, R);
-            project_out(m->act_a, L.k_cat, L.wo_cat, L.norm1);
+            project_out(m->act_a, L.k_cat, L.wo_cat, L.norm1, moe_next);
         } else {
             DeltaGeom dg = L.dg;
             dg.rec_off = m->run_rec_off[run];
@@ -2216,7 +2243,7 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             dim3 hgrid(R, (dg.H + 3) / 4);
             if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (float*)m->act_a, ldo, 1.0f, R);
             else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (bf16*)m->act_a, ldo, 1.0f, R);
-            project_out(m->act_a, ldo, L.wo_delta, L.norm1);
+            project_out(m->act_a, ldo, L.wo_delta, L.norm1, moe_next);
         }
         if (L.d.ff_kind == B200_FF_MOE) {
             // The operand is m->hn in both layer forms; the router's rows come first in w_up ([router | e0 up | ... | always-on up]).
@@ -2224,21 +2251,25 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             const b200_moe_desc& e = L.d.moe;
             const size_t es = elt(m);
             if (!post) rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
-            gemm(m, m->hn, W, L.w_up, e.experts, W, m->P, e.experts, R, 1.0f, EPI_STORE);
-            launch(m, lp_moe_route_kernel, dim3((R + 3) / 4), dim3(128), 0, (const float*)m->P, e.experts, e.experts, e.top, m->moe_w, m->moe_sel, m->moe_selw, R);
-            const int vn = m->f32 ? 4 : 8;
+            if (!moe_next) {
+                gemm(m, m->hn, W, L.w_up, e.experts, W, m->P, e.experts, R, 1.0f, EPI_STORE);
+                launch(m, lp_moe_route_kernel, dim3((R + 3) / 4), dim3(128), 0, (const float*)m->P, e.experts, e.experts, e.top, m->moe_w, m->moe_sel, m->moe_selw, R);
+            }
             const size_t hbytes = (size_t)R * W * es;
             const uint8_t* up_experts = (const uint8_t*)L.w_up + (size_t)e.experts * W * es;
-            if (m->use_fuse && R <= 2 * GV_ROWS && W % vn == 0 && e.expert_ff % vn == 0 && e.shared_ff % vn == 0 && hbytes <= 48 * 1024) {
+            bool normed = false;
+            if (moe_sel_ok) {
                 // few rows (decoding): kernels that walk each row's choices and read those experts' weights only
                 const int per_row = e.top * e.expert_ff + e.shared_ff;
                 dim3 ugrid(std::min((R * per_row + 7) / 8, 8 * 148)), dgrid(std::min((R * W + 7) / 8, 8 * 148));
+                const RowsTail t = few ? make_tail(L.norm2, nullptr) : RowsTail{};
+                normed = few;
                 if (m->f32) {
                     launch(m, lp_moe_up_sel_kernel<float>, ugrid, dim3(256), hbytes, (const float*)m->hn, (const float*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (float*)m->act_a);
-                    launch(m, lp_moe_down_sel_kernel<float>, dgrid, dim3(256), 0, (const float*)m->act_a, (const float*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y);
+                    launch(m, lp_moe_down_sel_kernel<float>, dgrid, dim3(256), 0, (const float*)m->act_a, (const float*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y, t);
                 } else {
                     launch(m, lp_moe_up_sel_kernel<bf16>, ugrid, dim3(256), hbytes, (const bf16*)m->hn, (const bf16*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (bf16*)m->act_a);
-                    launch(m, lp_moe_down_sel_kernel<bf16>, dgrid, dim3(256), 0, (const bf16*)m->act_a, (const bf16*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y);
+                    launch(m, lp_moe_down_sel_kernel<bf16>, dgrid, dim3(256), 0, (const bf16*)m->act_a, (const bf16*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y, t);
                 }
             } else if (m->use_fuse && R > 2 * GV_ROWS) {
                 // many rows: the (token, choice) pairs in expert order, one product pair per expert over its block of rows (the row
@@ -2266,17 +2297,18 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                 else launch(m, lp_moe_act_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (bf16*)m->act_a, R);
                 gemm(m, m->act_a, L.k_down, L.w_down, W, L.k_down, m->y, W, R, 1.0f, EPI_STORE);
             }
-            if (post) cast_x(m->y, L.norm2);
+            if (normed) {
+            } else if (post) cast_x(m->y, L.norm2);
             else launch(m, lp_add_rows_kernel, dim3((unsigned)(((size_t)R * W + 255) / 256)), dim3(256), 0, m->x, (const float*)m->y, (size_t)R * W);
         } else if (L.d.ff > 0 && L.d.ff_kind == B200_FF_GATED_GELU) {
             project_in(nullptr, L.norm2, L.w_up, L.n_up, m->P, L.n_up, EPI_STORE);
             const unsigned nb = (unsigned)(((size_t)R * L.d.ff + 255) / 256);
             if (m->f32) launch(m, lp_gated_gelu_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, (float*)m->act_a, L.d.ff, R);
             else launch(m, lp_gated_gelu_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, (bf16*)m->act_a, L.d.ff, R);
-            project_out(m->act_a, L.d.ff, L.w_down, L.norm2);
+            project_out(m->act_a, L.d.ff, L.w_down, L.norm2, nullptr);
         } else if (L.d.ff > 0) {
             project_in(nullptr, L.norm2, L.w_up, L.d.ff, m->act_a, L.d.ff, EPI_RELU2);
-            project_out(m->act_a, L.d.ff, L.w_down, L.norm2);
+            project_out(m->act_a, L.d.ff, L.w_down, L.norm2, nullptr);
         } else if (post && L.norm2) {
             cast_x(nullptr, L.norm2);
         }

@@ -52,45 +52,12 @@ __global__ void lp_gated_gelu_kernel(const float* __restrict__ P, int ldp, OutT*
     out[i] = from_f<OutT>(gelu_tanh_f(p[n]) * p[ff + n]);
 }
 
-// Router: one warp per row.  z = P[r][0 .. E) (f32 logits of the fused projection).  The `top` largest logits are taken one after
-// the other (of equal logits the lower index first); their weights are the softmax over the chosen logits only.  wts[r][e] is the
-// weight of expert e (0 when it is not chosen); sel[r][k] / selw[r][k] list the chosen experts in the order they were taken.
+// Router: one warp per row of the f32 logits P[r][0 .. E) (route_row, lp_rows_tail.cuh)
 __global__ void lp_moe_route_kernel(const float* __restrict__ P, int ldp, int E, int top, float* __restrict__ wts, int* __restrict__ sel,
                                     float* __restrict__ selw, int R) {
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (r >= R) return;
-    const float* z = P + (size_t)r * ldp;
-    float* w = wts + (size_t)r * E;
-    for (int e = lane; e < E; e += 32) w[e] = 0.0f;
-    __syncwarp();
-    float zmax = 0.0f, sum = 0.0f;
-    for (int k = 0; k < top; k++) {
-        float best = -INFINITY;
-        int bi = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = z[e];
-            if (w[e] == 0.0f && (v > best || (v == best && e < bi))) { best = v; bi = e; }   // (chosen experts carry a mark != 0)
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-        }
-        if (k == 0) zmax = best;
-        const float p = expf(best - zmax);
-        sum += p;
-        if (lane == 0) {
-            w[bi] = -1.0f - p;          // mark; turned into the weight below
-            sel[(size_t)r * top + k] = bi;
-            selw[(size_t)r * top + k] = p;
-        }
-        __syncwarp();
-    }
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32)
-        if (w[e] != 0.0f) w[e] = (-1.0f - w[e]) * inv;
-    for (int k = lane; k < top; k += 32) selw[(size_t)r * top + k] *= inv;
+    route_row(P + (size_t)r * ldp, E, top, wts + (size_t)r * E, sel + (size_t)r * top, selw + (size_t)r * top, lane);
 }
 
 // out[r][c] = relu(P[r][off + c])^2 * (weight of the expert that owns column c; 1 for the always-on expert's columns behind them)
@@ -153,7 +120,7 @@ __global__ void __launch_bounds__(256) lp_moe_up_sel_kernel(const T* __restrict_
 // y[r][c] = sum over the row's segments of down_e[c] . act segment; down_cat is [width][E eff + sff].  One warp per (row, c).
 template <typename T>
 __global__ void __launch_bounds__(256) lp_moe_down_sel_kernel(const T* __restrict__ act, const T* __restrict__ down_cat, const int* __restrict__ sel,
-                                                              int E, int top, int eff, int sff, int width, int R, float* __restrict__ y) {
+                                                              int E, int top, int eff, int sff, int width, int R, float* __restrict__ y, RowsTail tail) {
     constexpr int VN = Vec8<T>::N;
     const int lane = threadIdx.x & 31;
     const int per_row = top * eff + sff, kd = E * eff + sff;
@@ -178,6 +145,7 @@ __global__ void __launch_bounds__(256) lp_moe_down_sel_kernel(const T* __restric
         acc = wsum(acc);
         if (lane == 0) y[o] = acc;
     }
+    if (tail.on) rows_tail<T>(tail);
 }
 
 // Many rows: the (token, choice) pairs are put in expert order, so that every expert multiplies a contiguous block of rows.

@@ -19,12 +19,13 @@ struct PrepGeom {
 // One block per row.  Step 1: u = P + bias, y = causal convolution of u over time (inputs before the run's first row come from the
 // run's tail, zeros at the start of a sequence) into shared memory.  Step 2: per head of q and k (a warp each): rotate the first
 // rot_dims channels (channel 2i with 2i + 1).  Step 3: the norm (over the whole of q and of k, or a warp per head).  Step 4: q to
-// qbuf, k to the cache row, v (blended) to the cache row.
+// qbuf, k to the cache row, v (blended) to the cache row.  shift_tail: the step has one row per run and the block also moves the
+// run's tail on by this row (else lp_attn_conv_tail_kernel does it for the whole run afterwards).
 __global__ void __launch_bounds__(256) lp_attn_prep2_kernel(StepMeta sm, AttnGeom a, PrepGeom g, const float* __restrict__ P, int ldp,
                                                             const float* __restrict__ bias, const float* __restrict__ cw,
                                                             const float* __restrict__ qw, const float* __restrict__ kw,
                                                             const double* __restrict__ inv_freq, const float* __restrict__ lam_p,
-                                                            float* __restrict__ vsrc, float* __restrict__ qbuf) {
+                                                            float* __restrict__ vsrc, float* __restrict__ qbuf, int shift_tail) {
     extern __shared__ __align__(16) float ps[];
     float* y = ps;                              // [C]
     float* cs = ps + ((g.C + 3) & ~3);          // [rot_dims / 2] cos, then sin
@@ -32,7 +33,7 @@ __global__ void __launch_bounds__(256) lp_attn_prep2_kernel(StepMeta sm, AttnGeo
     __shared__ float red[2][8];
     const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int run = sm.row_run[r], pos = sm.row_pos[r], t = r - sm.run_start[run];
-    const float* tail = reinterpret_cast<const float*>(sm.run_rec[run] + g.rec_off);
+    float* tail = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off);
     const int nt = g.taps;
     for (int c = threadIdx.x; c < g.C; c += blockDim.x) {
         const float b = bias ? bias[c] : 0.0f;
@@ -44,6 +45,10 @@ __global__ void __launch_bounds__(256) lp_attn_prep2_kernel(StepMeta sm, AttnGeo
                 const int tt = t - (nt - 1) + i;
                 const float in = tt >= 0 ? P[(size_t)(r - t + tt) * ldp + c] + b : tail[(size_t)(nt - 1 + tt) * g.C + c];
                 v = fmaf(cw[(size_t)c * nt + i], in, v);
+            }
+            if (shift_tail && nt > 1) {   // every run has one row (decoding): the tail moves on by this input, channel by channel
+                for (int i = 0; i + 1 < nt - 1; i++) tail[(size_t)i * g.C + c] = tail[(size_t)(i + 1) * g.C + c];
+                tail[(size_t)(nt - 2) * g.C + c] = P[(size_t)r * ldp + c] + b;
             }
         }
         y[c] = v;
