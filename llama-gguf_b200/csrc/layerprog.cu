@@ -1940,6 +1940,13 @@ int lp_finalize(LpModel* m, std::string* err) {
             if ((rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
         }
     }
+    {   // the preparation kernel of the softmax mixer keeps a row's q, k, v in shared memory
+        size_t need = 0;
+        for (const LayerPlan& L : m->plan)
+            if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) need = std::max(need, (size_t)(((L.pg.C + 3) & ~3) + L.pg.rot_dims) * 4);
+        if (need > 200 * 1024) return lp_fail(err, B200_ERR_UNSUPPORTED, "softmax mixer: q, k and v of one token exceed 200 KB of shared memory");
+        if (need > 48 * 1024) LCU(cudaFuncSetAttribute(lp_attn_prep2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need));
+    }
     if (p.norm_weight_offset != 0.0f) {   // norm weights stored around zero: (offset + w) once, in f32
         std::vector<std::string> nm = {"final.norm"};
         for (int li = 0; li < p.n_layers; li++)
@@ -2261,7 +2268,7 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             if (moe_sel_ok) {
                 // few rows (decoding): kernels that walk each row's choices and read those experts' weights only
                 const int per_row = e.top * e.expert_ff + e.shared_ff;
-                dim3 ugrid(std::min((R * per_row + 7) / 8, 8 * 148)), dgrid(std::min((R * W + 7) / 8, 8 * 148));
+                dim3 ugrid(std::min((R * per_row + 7) / 8, 8 * 148)), dgrid(std::min((R * W + 1) / 2, 8 * 148));
                 const RowsTail t = few ? make_tail(L.norm2, nullptr) : RowsTail{};
                 normed = few;
                 if (m->f32) {

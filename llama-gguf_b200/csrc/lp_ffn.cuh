@@ -117,33 +117,49 @@ __global__ void __launch_bounds__(256) lp_moe_up_sel_kernel(const T* __restrict_
     }
 }
 
-// y[r][c] = sum over the row's segments of down_e[c] . act segment; down_cat is [width][E eff + sff].  One warp per (row, c).
+// y[r][c] = sum over the row's segments of down_e[c] . act segment; down_cat is [width][E eff + sff].  MD_SPLIT warps share one (row, c):
+// each takes every MD_SPLIT-th 16-byte group of every segment (more loads in flight per output: a decode step has only `width` of
+// them), the partial sums meet in shared memory and are added in warp order.
+constexpr int MD_SPLIT = 4;
 template <typename T>
 __global__ void __launch_bounds__(256) lp_moe_down_sel_kernel(const T* __restrict__ act, const T* __restrict__ down_cat, const int* __restrict__ sel,
                                                               int E, int top, int eff, int sff, int width, int R, float* __restrict__ y, RowsTail tail) {
-    constexpr int VN = Vec8<T>::N;
-    const int lane = threadIdx.x & 31;
-    const int per_row = top * eff + sff, kd = E * eff + sff;
-    for (int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); o < R * width; o += gridDim.x * (blockDim.x >> 5)) {
-        const int r = o / width, c = o - r * width;
-        const T* ar = act + (size_t)r * per_row;
-        const T* dr = down_cat + (size_t)c * kd;
+    constexpr int VN = Vec8<T>::N, GROUPS = 8 / MD_SPLIT;
+    __shared__ float part[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = warp / MD_SPLIT, sw = warp % MD_SPLIT;
+    const int per_row = top * eff + sff, kd = E * eff + sff, total = R * width;
+    for (int base = blockIdx.x * GROUPS; base < total; base += gridDim.x * GROUPS) {
+        const int o = base + grp;
         float acc = 0.0f;
-        for (int k = 0; k <= top; k++) {
-            const int e = k < top ? sel[(size_t)r * top + k] : E;
-            const int len = k < top ? eff : sff;
-            const T* w = dr + (size_t)e * eff;
-            const T* a = ar + (size_t)k * eff;
-            for (int i = lane * VN; i < len; i += 32 * VN) {
-                float wv[VN], xv[VN];
-                Vec8<T>::load(w + i, wv);
-                Vec8<T>::load(a + i, xv);
+        if (o < total) {
+            const int r = o / width, c = o - r * width;
+            const T* ar = act + (size_t)r * per_row;
+            const T* dr = down_cat + (size_t)c * kd;
+            for (int k = 0; k <= top; k++) {
+                const int e = k < top ? sel[(size_t)r * top + k] : E;
+                const int len = k < top ? eff : sff;
+                const T* w = dr + (size_t)e * eff;
+                const T* a = ar + (size_t)k * eff;
+#pragma unroll 4
+                for (int i = (sw * 32 + lane) * VN; i < len; i += MD_SPLIT * 32 * VN) {
+                    float wv[VN], xv[VN];
+                    Vec8<T>::load(w + i, wv);
+                    Vec8<T>::load(a + i, xv);
 #pragma unroll
-                for (int j = 0; j < VN; j++) acc = fmaf(wv[j], xv[j], acc);
+                    for (int j = 0; j < VN; j++) acc = fmaf(wv[j], xv[j], acc);
+                }
             }
         }
         acc = wsum(acc);
-        if (lane == 0) y[o] = acc;
+        if (lane == 0) part[warp] = acc;
+        __syncthreads();
+        if (o < total && sw == 0 && lane == 0) {
+            float t = part[grp * MD_SPLIT];
+#pragma unroll
+            for (int i = 1; i < MD_SPLIT; i++) t += part[grp * MD_SPLIT + i];
+            y[o] = t;
+        }
+        __syncthreads();
     }
     if (tail.on) rows_tail<T>(tail);
 }
