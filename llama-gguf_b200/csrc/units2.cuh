@@ -5,7 +5,7 @@
 // unit_q80; what changes is the loop nest.  The first generation loads the B operands (the int8 planes of x) of a whole
 // 256-element unit up front (32 registers) and unrolls both 16-row blocks: ~200 live registers.  Here the row-block loop is a
 // run-time loop (its bounds let a job compute one 16-row block only) and the lane tables are three words (LaneT), which
-// brings the same unit to ~80 live registers at the same ~270 instructions.  Measured dead ends of this round, kept for
+// brings the same unit to ~80 live registers at the same ~270 instructions.  Measured dead ends, kept for
 // the record: splitting a unit between two warps by K halves (343 instructions per unit: scale decoding duplicated) or by
 // row blocks (388: B operand loads duplicated); fully unrolled Q6_K variants (6 copies, 40 KB of hot code: instruction-cache bound).
 // Reference arithmetic: src/backend/cpu/simd.rs:978-1146 (dot_q4_k / dot_q5_k / dot_q6_k / dot_q8_0).

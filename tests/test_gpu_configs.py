@@ -1,6 +1,6 @@
 """Parity at the shapes BASELINE.json names, not miniatures (VERDICT r1 "parity at real config shapes"), plus the tie rules of
 the greedy pick (src/main.rs:1816-1821: LAST maximal index) and of the MoE router (src/model/moe.rs:168: stable sort, lowest
-index first) exercised on the device, the Backend methods exported this round and the opt-in prefill queue.
+index first) exercised on the device, the exported Backend methods and the opt-in prefill queue.
 Tolerance: logits within 1e-3 relative (max|a-b| / max|b|), greedy token sequences identical (north star)."""
 import os
 

@@ -451,8 +451,8 @@ def test_bad_arguments(b200):
 
 
 # ---------------------------------------------------------------------------------------------------- kernels against their plain forms
-@pytest.mark.parametrize("kind,dims", [("window", (16, 24, 11)), ("window", (32, 40, 70)), ("chunk", (96, 48, 23)), ("chunk", (128, 128, 64)),
-                                       ("window", (64, 48, 64))])
+@pytest.mark.parametrize("kind,dims", [("window", (16, 24, 11)), ("window", (32, 40, 70)), ("chunk", (96, 56, 23)), ("chunk", (128, 128, 64)),
+                                       ("window", (64, 40, 64))])
 def test_tile_attention_against_warp_attention(b200, monkeypatch, kind, dims):
     # bf16 prompts take the tensor-pipe attention kernel when the head sizes allow it; the warp kernel computes the same thing in f32.
     # Windows and chunks that end inside, at and across key tiles of 64; several unequal runs in one step, one of them continued
