@@ -52,7 +52,7 @@ def mefurax_config(s, span=1024):
         if ch == "a":
             m["conv"] = 4
         else:
-            m.update(rot={"dims": 64, "base": 500000.0}, softcap=30.0)
+            m.update(rot={"dims": 64, "base": 10000.0}, softcap=50.0)
         layers.append({"type": "attention" if ch == "a" else "attention_2", "mixer": m, "mlp": mlp})
     return {"architecture": "Mefurax", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6}, "postln_alpha": 2.0, "layers": layers}
 

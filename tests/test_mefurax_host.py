@@ -46,7 +46,7 @@ def test_small_pieces():
     idx, wts = O.route(np.array([0.0, 1.0, 3.0]), 3)
     assert idx == [2, 1, 0] and abs(sum(wts) - 1) < 1e-12
     assert abs(O.distance_slope(7, 8) - 2.0 ** -8) < 1e-15 and abs(O.distance_slope(0, 8) - 0.5) < 1e-15
-    assert abs(O.soft_cap(1000.0, 30.0) - 30.0) < 1e-9
+    assert abs(O.soft_cap(1000.0, 12.5) - 12.5) < 1e-9
     assert abs(O.gelu_tanh(np.array([1.0]))[0] - 0.8411919906082768) < 1e-12
 
 
